@@ -504,6 +504,61 @@ int b200_compute_position(int64_t* positions, int32_t* extend_start_loc,
                           const int32_t* extend_prefix_lens, const int32_t* extend_seq_lens, int bs,
                           void* stream);
 
+/* ---- sequence-model layers with a 32-bit residual stream ------------------------------------- */
+/* Row RMS norm in fp32 over a fp32 residual x [T, W]: h = x / sqrt(mean(x^2) + eps) * (*gain)
+ * (* weight[d]); gain / weight may be NULL (= 1).  With `mu` also the token-shifted copy
+ * hm = h + (h_prev - h) * mu[d]: h_prev is the h of the previous token of the same sequence — the
+ * row before it in this batch, the row state[slot[b]] when the token opens its portion, zeros at
+ * position 0 — and state[slot[b]] is replaced by the h of the portion's last token.
+ * tok_pos / tok_b: position and batch entry of every token; ext_start / ext_len: first row and row
+ * count of every batch entry.  out_h may be NULL when mu is given.  out_dtype: BF16 / F16 / F32.   */
+int b200_scalar_rmsnorm_shift(const float* x, int64_t ldx, const float* gain, const float* weight,
+                              float eps, const float* mu, float* state, int64_t ld_state,
+                              const int* tok_pos, const int* tok_b, const int* ext_start,
+                              const int* ext_len, const int64_t* slot, void* out_h, int64_t ldh,
+                              void* out_hm, int64_t ldm, int T, int W, int out_dtype, void* stream);
+/* x[t] += a[t] + b[t] + sum_k topk_w[t,k] * y[t*top + k] + gate[t] * s[t]; a, b, y, s (dtype) are
+ * optional, gate NULL = 1.  The sum is formed in fp32.                                            */
+int b200_residual_combine(float* x, int64_t ldx, const void* a, int64_t lda, const void* b,
+                          int64_t ldb, const void* y, int64_t ldy, const float* topk_w, int top,
+                          const void* s, int64_t lds, const float* gate, int T, int W, int dtype,
+                          void* stream);
+/* out[t, d] = act(z[t, d]) * z[t, D + d]; kind 0 = silu, 1 = gelu (tanh form).                    */
+int b200_act_and_mul(const void* z, int64_t ldz, void* out, int64_t ldo, int T, int D, int kind,
+                     int dtype, void* stream);
+/* Latent attention, step 1: cq = RMSnorm(qraw) * wq; pool row loc[t] = [RMSnorm(kvraw[:R]) * wkv |
+ * rotary(kvraw[R:R+rot])] with the interleaved pairing (2i, 2i+1) on the first rot_dims
+ * coordinates, angle tok_pos * inv_freq[i] in fp32.  Either half may be skipped (NULL).           */
+int b200_latent_prep(const void* qraw, int64_t ldq, int QR, const float* wq, void* cq, int64_t ldcq,
+                     const void* kvraw, int64_t ldkv, int R, int rot, int rot_dims, const float* wkv,
+                     const float* inv_freq, const int* tok_pos, const int64_t* loc, void* cache,
+                     int64_t ldc, float eps, int T, int dtype, void* stream);
+/* Latent attention, step 2 (absorbed form) over pool rows [c | kr]: for token t of batch entry
+ * tok_b[t] at position p, keys j in [max(0, p - window + 1), p] (window <= 0: [0, p]) found through
+ * req_to_token[req_pool[b], j]; score = (q_lat[t,h] . c_j + rotary(q_raw[t,h][q_rot_off:]) . kr_j)
+ * * scale, softmax, out[t,h] = sum_j p_j c_j.  fp32 scores / weights / accumulation.  max_keys is a
+ * hint (longest key range in the batch, 0 = unknown).                                             */
+int b200_latent_attn(const float* q_lat, int64_t ldql_t, int64_t ldql_h, const void* q_raw,
+                     int64_t ldqr_t, int64_t ldqr_h, int q_rot_off, const void* cache, int64_t ldc,
+                     const int* r2t, int64_t ld_r2t, const int64_t* req_pool, const int* tok_pos,
+                     const int* tok_b, const float* inv_freq, int rot_dims, int T, int H, int R,
+                     int rot, int window, int max_keys, float scale, void* out, int64_t ldo_t,
+                     int64_t ldo_h, int dtype, void* stream);
+/* Router: z = wr h + br (fp32), the `top` largest logits (ties: lowest index), weights = softmax
+ * over the chosen logits; gate[t] = sigmoid(wsg . h) when wsg is given.                           */
+int b200_moe_route(const void* h, int64_t ldh, const float* wr, const float* br, int E, int W,
+                   int top, const float* wsg, int* ids, float* wts, float* gate, int T, int dtype,
+                   void* stream);
+/* Stable sort of rows 0..N-1 by ids[row]: offsets [E + 1], sorted_rows [N].                       */
+int b200_moe_align(const int* ids, int N, int E, int* offsets, int* sorted_rows, void* stream);
+/* Per expert e: rows offsets[e]..offsets[e+1] times w[e]^T (w [E][(2)Nout, K]).  gated: A row =
+ * a[sorted_rows[m] / top], out[m] = act(gate half) * up half; else A row = a[m] and the result goes
+ * to out[sorted_rows[m]].                                                                         */
+int b200_moe_grouped_gemm(const void* a, int64_t lda, const void* w, int64_t ldw,
+                          int64_t w_expert_stride, const int* offsets, const int* sorted_rows, int E,
+                          int top, int rows, int Nout, int K, void* out, int64_t ldo, int gated,
+                          int act, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

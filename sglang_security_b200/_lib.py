@@ -149,6 +149,28 @@ _SIGNATURES = {
     "b200_w4a16_repack_gptq": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "b200_w4a16_gemm": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_scalar_rmsnorm_shift": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p,
+                                          c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int,
+                                          c_int, c_void_p]),
+    "b200_residual_combine": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                      c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int64, c_void_p,
+                                      c_int, c_int, c_int, c_void_p]),
+    "b200_act_and_mul": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int,
+                                 c_void_p]),
+    "b200_latent_prep": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p,
+                                 c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_int64, c_float, c_int, c_int, c_void_p]),
+    "b200_latent_attn": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int,
+                                 c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                 c_void_p, c_int64, c_int64, c_int, c_void_p]),
+    "b200_moe_route": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "b200_moe_align": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200_moe_grouped_gemm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p,
+                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int64,
+                                      c_int, c_int, c_int, c_void_p]),
 }
 
 

@@ -75,6 +75,15 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+def ensure_built() -> Path:
+    """Build the library if it is missing or older than its sources (first use in a fresh checkout)."""
+    if LIB_PATH.exists():
+        newest = max([p.stat().st_mtime for p in CSRC.glob("*.cu")] + [_newest_dep_mtime()])
+        if LIB_PATH.stat().st_mtime >= newest:
+            return LIB_PATH
+    return build()
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose=True)
     print(path)

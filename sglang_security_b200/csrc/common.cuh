@@ -206,8 +206,16 @@ template <>
 __device__ __forceinline__ __half from_float<__half>(float x) {
   return __float2half_rn(x);
 }
+template <>
+__device__ __forceinline__ float from_float<float>(float x) {
+  return x;
+}
 template <typename T>
 __device__ __forceinline__ float to_float(T x);
+template <>
+__device__ __forceinline__ float to_float<float>(float x) {
+  return x;
+}
 template <>
 __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 x) {
   return __bfloat162float(x);

@@ -1,0 +1,263 @@
+// Mixture-of-experts feed-forward, device side only (no host read of the routing result):
+//   moe_route        : router logits z = W_r h + b in fp32, the `top` largest (ties: lowest index),
+//                      weights = softmax over the chosen logits; optionally the per-token gate
+//                      sigmoid(w_sg . h) of a shared expert.  One warp per token.
+//   moe_align        : stable counting sort of the (token, choice) rows by expert -> row offsets per
+//                      expert and the sorted row list.
+//   moe_grouped_gemm : for every expert, rows[offsets[e] : offsets[e+1]] x W[e]^T with fp32
+//                      accumulation.  GATED: A rows are gathered from the token activations, both
+//                      halves of the fused [gate; up] weight are multiplied in one pass and
+//                      act(gate) * up is stored in sorted order; otherwise A is that intermediate and
+//                      the result is scattered back to row t * top + k for the weighted combine.
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int kMaxExpertsPerLane = 8;  // experts <= 256
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* __restrict__ h, int64_t ldh, const float* __restrict__ wr,
+                 const float* __restrict__ br, int E, int W, int top, const float* __restrict__ wsg,
+                 int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ gate, int Tn) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= Tn) return;
+  const T* row = h + t * ldh;
+  float z[kMaxExpertsPerLane];
+#pragma unroll
+  for (int i = 0; i < kMaxExpertsPerLane; ++i) z[i] = -INFINITY;
+  for (int e = 0; e < E; ++e) {
+    const float* w = wr + static_cast<int64_t>(e) * W;
+    float s = 0.f;
+    for (int d = lane; d < W; d += 32) s = fmaf(w[d], to_float<T>(row[d]), s);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    s += br ? br[e] : 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i)
+      if (e == lane + 32 * i) z[i] = s;
+  }
+  if (wsg && gate) {
+    float s = 0.f;
+    for (int d = lane; d < W; d += 32) s = fmaf(wsg[d], to_float<T>(row[d]), s);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) gate[t] = 1.0f / (1.0f + expf(-s));
+  }
+  float zmax = 0.f, sum = 0.f, mine = 0.f;  // lane k keeps the k-th chosen logit
+  for (int k = 0; k < top; ++k) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+      const int e = lane + 32 * i;
+      if (e < E && (z[i] > bv || (z[i] == bv && e < bi))) {
+        bv = z[i];
+        bi = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (k == 0) zmax = bv;
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i)
+      if (bi == lane + 32 * i) z[i] = -INFINITY;
+    const float p = expf(bv - zmax);
+    sum += p;
+    if (lane == k) mine = p;
+    if (lane == 0) ids[t * top + k] = bi;
+  }
+  if (lane < top) wts[t * top + lane] = mine / sum;
+}
+
+__global__ void __launch_bounds__(1024)
+moe_align_kernel(const int* __restrict__ ids, int N, int E, int* __restrict__ offsets,
+                 int* __restrict__ sorted_rows) {
+  extern __shared__ int cnt[];  // [E + 1]
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < N; i += blockDim.x) atomicAdd(&cnt[ids[i] + 1], 1);
+  __syncthreads();
+  if (threadIdx.x == 0)
+    for (int e = 0; e < E; ++e) cnt[e + 1] += cnt[e];
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = cnt[e];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int e = warp; e < E; e += nw) {
+    int base = cnt[e];
+    for (int i0 = 0; i0 < N; i0 += 32) {
+      const int i = i0 + lane;
+      const bool hit = i < N && ids[i] == e;
+      const unsigned mask = __ballot_sync(0xffffffffu, hit);
+      if (hit) sorted_rows[base + __popc(mask & ((1u << lane) - 1u))] = i;
+      base += __popc(mask);
+    }
+  }
+}
+
+__device__ __forceinline__ float moe_act(float z, int kind) {
+  if (kind == 0) return z / (1.0f + expf(-z));
+  const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+  return 0.5f * z * (1.0f + tanhf(u));
+}
+
+constexpr int kGM = 32, kGN = 64, kGK = 32;
+
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_grouped_gemm_kernel(const T* __restrict__ a, int64_t lda, const T* __restrict__ w, int64_t ldw,
+                        int64_t w_expert_stride, const int* __restrict__ offsets,
+                        const int* __restrict__ sorted_rows, int E, int top, int Nout, int K,
+                        T* __restrict__ out, int64_t ldo, int act) {
+  __shared__ float As[kGM][kGK + 1];
+  __shared__ float Bs[(GATED ? 2 : 1) * kGN][kGK + 1];
+  __shared__ int rows[kGM];
+  // which expert and which of its row tiles this CTA has
+  int e = 0, tile = blockIdx.x, lo = 0, hi = 0;
+  for (; e < E; ++e) {
+    lo = offsets[e];
+    hi = offsets[e + 1];
+    const int nt = (hi - lo + kGM - 1) / kGM;
+    if (tile < nt) break;
+    tile -= nt;
+  }
+  if (e >= E) return;
+  const int m0 = lo + tile * kGM, mcount = min(kGM, hi - m0);
+  const int n0 = blockIdx.y * kGN;
+  if (threadIdx.x < kGM) {
+    int r = -1;
+    if (threadIdx.x < mcount) r = sorted_rows[m0 + threadIdx.x];
+    rows[threadIdx.x] = r;
+  }
+  __syncthreads();
+  const T* we = w + e * w_expert_stride;
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  float acc[2][4], acc2[2][4];
+#pragma unroll
+  for (int r = 0; r < 2; ++r)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[r][c] = acc2[r][c] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += kGK) {
+    for (int idx = threadIdx.x; idx < kGM * kGK; idx += 256) {
+      const int r = idx / kGK, k = idx - r * kGK;
+      float v = 0.f;
+      if (r < mcount && k0 + k < K) {
+        const int64_t src = GATED ? rows[r] / top : m0 + r;
+        v = to_float<T>(a[src * lda + k0 + k]);
+      }
+      As[r][k] = v;
+    }
+    for (int idx = threadIdx.x; idx < (GATED ? 2 : 1) * kGN * kGK; idx += 256) {
+      const int r = idx / kGK, k = idx - r * kGK;
+      const int half = r / kGN, n = n0 + (r - half * kGN);
+      float v = 0.f;
+      if (n < Nout && k0 + k < K) v = to_float<T>(we[(static_cast<int64_t>(half) * Nout + n) * ldw + k0 + k]);
+      Bs[r][k] = v;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int k = 0; k < kGK; ++k) {
+      const float a0 = As[ty * 2][k], a1 = As[ty * 2 + 1][k];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float b = Bs[tx + 16 * c][k];
+        acc[0][c] = fmaf(a0, b, acc[0][c]);
+        acc[1][c] = fmaf(a1, b, acc[1][c]);
+        if (GATED) {
+          const float b2 = Bs[kGN + tx + 16 * c][k];
+          acc2[0][c] = fmaf(a0, b2, acc2[0][c]);
+          acc2[1][c] = fmaf(a1, b2, acc2[1][c]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int lr = ty * 2 + r;
+    if (lr >= mcount) continue;
+    const int64_t orow = GATED ? m0 + lr : rows[lr];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int n = n0 + tx + 16 * c;
+      if (n >= Nout) continue;
+      const float v = GATED ? moe_act(acc[r][c], act) * acc2[r][c] : acc[r][c];
+      out[orow * ldo + n] = from_float<T>(v);
+    }
+  }
+}
+
+}  // namespace b200
+
+extern "C" int b200_moe_route(const void* h, int64_t ldh, const float* wr, const float* br, int E,
+                              int W, int top, const float* wsg, int* ids, float* wts, float* gate,
+                              int T, int dtype, void* stream) {
+  using namespace b200;
+  if (T == 0) return 0;
+  B200_REQUIRE(h && wr && ids && wts, "b200_moe_route: null pointer");
+  B200_REQUIRE(E > 0 && E <= 32 * kMaxExpertsPerLane && top > 0 && top <= E && top <= 32 && W > 0,
+               "b200_moe_route: experts %d (max %d), top %d", E, 32 * kMaxExpertsPerLane, top);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const dim3 grid(ceil_div(T, 4));
+#define LAUNCH(TT)                                                                                   \
+  launch_kernel(moe_route_kernel<TT>, grid, dim3(128), 0, st, 1, 0, static_cast<const TT*>(h), ldh,  \
+                wr, br, E, W, top, wsg, ids, wts, gate, T)
+  if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
+  else if (dtype == B200_F16) LAUNCH(__half);
+  else if (dtype == B200_F32) LAUNCH(float);
+  else B200_REQUIRE(false, "b200_moe_route: dtype %d", dtype);
+#undef LAUNCH
+  B200_CHECK_LAUNCH("moe_route_kernel");
+  return 0;
+}
+
+extern "C" int b200_moe_align(const int* ids, int N, int E, int* offsets, int* sorted_rows,
+                              void* stream) {
+  using namespace b200;
+  B200_REQUIRE(ids && offsets && sorted_rows && N >= 0 && E > 0 && E <= 4096, "b200_moe_align: bad arguments");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  launch_kernel(moe_align_kernel, dim3(1), dim3(1024), static_cast<size_t>(E + 1) * 4, st, 1, 0, ids,
+                N, E, offsets, sorted_rows);
+  B200_CHECK_LAUNCH("moe_align_kernel");
+  return 0;
+}
+
+extern "C" int b200_moe_grouped_gemm(const void* a, int64_t lda, const void* w, int64_t ldw,
+                                     int64_t w_expert_stride, const int* offsets,
+                                     const int* sorted_rows, int E, int top, int rows, int Nout, int K,
+                                     void* out, int64_t ldo, int gated, int act, int dtype,
+                                     void* stream) {
+  using namespace b200;
+  if (rows == 0) return 0;
+  B200_REQUIRE(a && w && offsets && sorted_rows && out, "b200_moe_grouped_gemm: null pointer");
+  B200_REQUIRE(E > 0 && top > 0 && rows > 0 && Nout > 0 && K > 0 && (act == 0 || act == 1),
+               "b200_moe_grouped_gemm: bad sizes");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // every expert can leave one partly filled row tile
+  const dim3 grid(ceil_div(rows, kGM) + min(E, rows), ceil_div(Nout, kGN));
+#define LAUNCH(TT, G)                                                                                \
+  launch_kernel(moe_grouped_gemm_kernel<TT, G>, grid, dim3(256), 0, st, 1, 0,                        \
+                static_cast<const TT*>(a), lda, static_cast<const TT*>(w), ldw, w_expert_stride,     \
+                offsets, sorted_rows, E, top, Nout, K, static_cast<TT*>(out), ldo, act)
+#define BY_G(TT)          \
+  do {                    \
+    if (gated) LAUNCH(TT, true); \
+    else LAUNCH(TT, false);      \
+  } while (0)
+  if (dtype == B200_BF16) BY_G(__nv_bfloat16);
+  else if (dtype == B200_F16) BY_G(__half);
+  else if (dtype == B200_F32) BY_G(float);
+  else B200_REQUIRE(false, "b200_moe_grouped_gemm: dtype %d", dtype);
+#undef BY_G
+#undef LAUNCH
+  B200_CHECK_LAUNCH("moe_grouped_gemm_kernel");
+  return 0;
+}

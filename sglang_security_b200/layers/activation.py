@@ -55,3 +55,26 @@ class SiluAndMul(nn.Module):
                  torch.empty((m, d // 128), device=x.device, dtype=torch.float32))
             _call(x2, d, None, q, s, 2)
         return q, s
+
+
+class GatedActAndMul(nn.Module):
+    """act(x[..., :d]) * x[..., d:] for bf16 / f16 / fp32 rows; act is "silu" or "gelu_tanh"
+    (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))).  One launch of b200_act_and_mul."""
+
+    KINDS = {"silu": 0, "gelu_tanh": 1}
+
+    def __init__(self, act: str):
+        super().__init__()
+        if act not in self.KINDS:
+            raise ValueError(f"unknown activation {act!r}")
+        self.kind = self.KINDS[act]
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        d = x.shape[-1] // 2
+        x2 = _rows(x)
+        out = torch.empty((x2.shape[0], d), dtype=x.dtype, device=x.device)
+        rc = _lib.load().b200_act_and_mul(x2.data_ptr(), x2.stride(0), out.data_ptr(), out.stride(0),
+                                          x2.shape[0], d, self.kind, _lib.dtype_code(x2.dtype),
+                                          _lib.current_stream())
+        _lib.check(rc, "b200_act_and_mul")
+        return out.view(x.shape[:-1] + (d,))

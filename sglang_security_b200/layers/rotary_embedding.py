@@ -168,3 +168,19 @@ def get_rope(head_size: int, rotary_dim: int, max_position: int, base: float,
                                      rope_scaling["high_freq_factor"],
                                      rope_scaling["original_max_position_embeddings"])
     raise NotImplementedError(f"rope_scaling type {kind!r} is not built (only None/'default'/'llama3')")
+
+
+class InterleavedRotary(nn.Module):
+    """Rotary positions in the interleaved pairing: coordinate 2i turns with 2i+1, i < dims / 2, by the
+    angle position * base^(-2i / dims).  Holds only the fp32 frequency table; the kernels that use it
+    (csrc/latent_attn.cu) form angle, sine and cosine in fp32 from the integer position, so there is no
+    table bounded by a maximum position."""
+
+    def __init__(self, dims: int, base: float):
+        super().__init__()
+        if dims % 2:
+            raise ValueError("rotary dims must be even")
+        self.dims, self.base = int(dims), float(base)
+        inv = torch.tensor([self.base ** (-2.0 * i / self.dims) for i in range(self.dims // 2)],
+                           dtype=torch.float64).to(torch.float32)
+        self.register_buffer("inv_freq", inv, persistent=False)

@@ -68,5 +68,14 @@ class ForwardBatch:
     token_to_kv_pool: Any = None
     attn_backend: Any = None
     spec_info: Any = None
+    # per-token / per-entry int32 tables for kernels that walk a mixed batch token by token
+    # (built by managers/schedule_batch.py): position and batch entry of every token, first row and
+    # row count of every entry; max_seq_len = longest sequence in the batch (host int)
+    tok_pos: Optional[torch.Tensor] = None
+    tok_b: Optional[torch.Tensor] = None
+    ext_start: Optional[torch.Tensor] = None
+    ext_len: Optional[torch.Tensor] = None
+    max_seq_len: int = 0
+    state_pool: Any = None
     encoder_lens: Optional[torch.Tensor] = None
     extra: dict = field(default_factory=dict)
