@@ -90,6 +90,9 @@ class PagedTokenToKVPoolAllocator:
         self.num_pages = size // page_size
         self._kvcache = kvcache
         self.ret_values = torch.empty((), dtype=torch.int64, device=self.device)
+        # stands in for an EMPTY free list (a null pointer is refused by the C-ABI): a step that only
+        # fills the open pages of its requests takes no page and never reads it
+        self._no_pages = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.clear()
 
     def available_size(self) -> int:
@@ -107,6 +110,9 @@ class PagedTokenToKVPoolAllocator:
         return (out_pages[:, None] * self.page_size
                 + torch.arange(self.page_size, device=self.device)).reshape(-1)
 
+    def _free_pages_ptr(self) -> int:
+        return (self.free_pages if self.free_pages.numel() else self._no_pages).data_ptr()
+
     def alloc_extend(self, prefix_lens: torch.Tensor, seq_lens: torch.Tensor,
                      last_loc: torch.Tensor, extend_num_tokens: int):
         bs = len(prefix_lens)
@@ -114,7 +120,7 @@ class PagedTokenToKVPoolAllocator:
         pre, seq, last = _i64(prefix_lens), _i64(seq_lens), _i64(last_loc)
         rc = _lib.load().b200_alloc_extend(
             pre.data_ptr(), seq.data_ptr(), last.data_ptr(),
-            self.free_pages.data_ptr(), out_indices.data_ptr(), self.ret_values.data_ptr(), bs,
+            self._free_pages_ptr(), out_indices.data_ptr(), self.ret_values.data_ptr(), bs,
             self.page_size, _lib.current_stream())
         _lib.check(rc, "b200_alloc_extend")
         merged_value = self.ret_values.item()
@@ -129,7 +135,7 @@ class PagedTokenToKVPoolAllocator:
         out_indices = torch.empty((bs,), dtype=torch.int64, device=self.device)
         seq, last = _i64(seq_lens), _i64(last_loc)
         rc = _lib.load().b200_alloc_decode(
-            seq.data_ptr(), last.data_ptr(), self.free_pages.data_ptr(),
+            seq.data_ptr(), last.data_ptr(), self._free_pages_ptr(),
             out_indices.data_ptr(), self.ret_values.data_ptr(), bs, self.page_size,
             _lib.current_stream())
         _lib.check(rc, "b200_alloc_decode")
