@@ -130,6 +130,7 @@ class DesiraxForCausalLM(nn.Module):
                 if not m or int(m.group(1)) >= len(self.layers):
                     raise ValueError(f"unexpected tensor {name!r}")
                 self._load_layer_tensor(self.layers[int(m.group(1))], m.group(2), w, pending)
+        self._check_complete(seen)
         for (lid, what), parts in pending.items():      # fused projections wait for all their parts
             layer = self.layers[lid]
             if what == "down":
@@ -140,7 +141,6 @@ class DesiraxForCausalLM(nn.Module):
                 layer.moe.shared.load(parts["gate"], parts["up"], parts["down"])
             else:
                 layer.moe.experts.load_expert(what, parts["gate"], parts["up"], parts["down"])
-        self._check_complete(seen)
 
     def _load_layer_tensor(self, layer: DesiraxLayer, key: str, w: torch.Tensor, pending) -> None:
         lid = layer.layer_id

@@ -1,0 +1,200 @@
+"""Desirax through the engine (loader, ModelRunner, pools, scheduler) against the plain restatement:
+whole prompts, token-by-token decoding, portions down to two tokens, unequal requests in one batch,
+pages and request slots that are freed and used again, window edges made visible, long decoding, and
+greedy generation through Engine.generate."""
+import pytest
+import torch
+
+import desirax_plain as P
+import desirax_util as U
+
+pytestmark = pytest.mark.gpu
+
+CONFIGS = {
+    # dense first, experts after, the last two layers read layer 1's latent
+    "a": lambda: U.config([(U.mixer(window=9), U.dense(48)), (U.mixer(window=9), U.moe(5, 2, 24, 16)),
+                           (U.mixer(window=9, kv_from=1), U.moe(5, 2, 24, 16)),
+                           (U.mixer(window=9, kv_from=1), None)], vocab=97, width=40),
+    # other sizes; layers differ from one another; top 1; no shared expert; a layer without window
+    "b": lambda: U.config([(U.mixer(heads=4, dim=16, rot_dim=16, vdim=24, kv_rank=64, q_rank=32, window=20,
+                                    base=500.0, rot_dims=8), U.moe(9, 1, 40, None)),
+                           (U.mixer(heads=2, dim=40, rot_dim=4, vdim=8, kv_rank=32, q_rank=40, window=None),
+                            U.dense(72)),
+                           (U.mixer(heads=4, dim=16, rot_dim=16, vdim=24, kv_rank=64, q_rank=32, window=70,
+                                    base=500.0, rot_dims=8, kv_from=0), U.moe(3, 3, 16, 56))],
+                          vocab=131, width=72, eps=1e-3),
+    # one head, window of one token (a token sees itself only), window two
+    "c": lambda: U.config([(U.mixer(heads=1, dim=8, rot_dim=2, vdim=8, kv_rank=8, q_rank=8, window=1), U.dense(16)),
+                           (U.mixer(heads=1, dim=8, rot_dim=2, vdim=8, kv_rank=8, q_rank=8, window=2), None)],
+                          vocab=33, width=24),
+}
+
+
+def _model(tmp_path, name, seed=0, sharp=False):
+    cfg = CONFIGS[name]()
+    if sharp:        # a peaked softmax: one key more or less inside a window moves the logits a lot
+        for L in cfg["layers"]:
+            L["mixer"]["scale"] *= 6.0
+    w = U.random_weights(cfg, seed)
+    return cfg, w, U.write_model(str(tmp_path / name), cfg, w)
+
+
+def _tokens(cfg, n, seed):
+    return torch.randint(0, cfg["vocab"], (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+TOL = {torch.float32: 1e-4, torch.bfloat16: 6e-2}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_whole_prompt_matches_plain_model(tmp_path, name, dtype):
+    cfg, w, folder = _model(tmp_path, name)
+    toks = _tokens(cfg, 150, 1)
+    want = P.forward(cfg, w, toks)
+    d = U.Driver(folder, dtype)
+    d.step([("r", toks)], end=["r"])
+    assert U.rel_err(d.result("r"), want, dtype) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_layer_outputs_match_plain_model_fp32(tmp_path, name):
+    from sglang_security_b200.managers.schedule_batch import Req, StepItem
+
+    cfg, w, folder = _model(tmp_path, name)
+    toks = _tokens(cfg, 40, 2)
+    want = []
+    P.forward(cfg, w, toks, layer_outputs=want)
+    d = U.Driver(folder, torch.float32)
+    req = Req(rid="x", input_ids=list(toks))
+    d.runner.admit(req)
+    got = []
+    d.sched.run_step([StepItem(req, list(toks), want=[0])], layer_hook=lambda i, x: got.append(x.double().cpu().clone()))
+    assert len(got) == len(want)
+    for g, t in zip(got, want):
+        assert (g - t).abs().max() <= 2e-5 * t.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_prefill_then_token_by_token_decoding(tmp_path, name, dtype):
+    """Most of the prompt in one step, then 90 single tokens: the windows (9, 20, 70) pass over decoded
+    tokens, 64-token pages are crossed, and the token-shift state is carried step to step."""
+    cfg, w, folder = _model(tmp_path, name, sharp=True)
+    toks = _tokens(cfg, 150, 3)
+    want = P.forward(cfg, w, toks)
+    d = U.Driver(folder, dtype)
+    d.step([("r", toks[:60])])
+    for t in toks[60:]:
+        d.step([("r", [t])])
+    assert U.rel_err(d.result("r"), want, dtype) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("cut", [[2] * 40, [1] * 12 + [7, 2, 64, 3, 33, 2, 1, 1], [63, 1, 1, 65, 2]])
+def test_portions_of_several_sizes(tmp_path, dtype, cut):
+    cfg, w, folder = _model(tmp_path, "a", sharp=True)
+    toks = _tokens(cfg, sum(cut), 4)
+    want = P.forward(cfg, w, toks)
+    d = U.Driver(folder, dtype)
+    at = 0
+    for n in cut:
+        d.step([("r", toks[at:at + n])])
+        at += n
+    assert U.rel_err(d.result("r"), want, dtype) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_unequal_requests_in_one_batch_and_reused_pages_and_slots(tmp_path, name, dtype):
+    """Four live requests at most, a pool of 6 pages: portions of some beside single tokens of others;
+    finished requests give their pages and slots to later ones.  Every request must come out as if
+    it had run alone."""
+    cfg, w, folder = _model(tmp_path, name, seed=5)
+    lens = {"p": 130, "q": 67, "r": 3, "s": 90, "t": 64, "u": 100}
+    toks = {k: _tokens(cfg, n, 10 + i) for i, (k, n) in enumerate(lens.items())}
+    want = {k: P.forward(cfg, w, v) for k, v in toks.items()}
+    d = U.Driver(folder, dtype, max_tokens=6 * 64, max_requests=4)
+    at = {k: 0 for k in toks}
+
+    def go(*parts):
+        portions, end = [], []
+        for k, n in parts:
+            portions.append((k, toks[k][at[k]:at[k] + n]))
+            at[k] += n
+            if at[k] == lens[k]:
+                end.append(k)
+        d.step(portions, end)
+
+    go(("p", 50), ("q", 2), ("r", 1))
+    go(("p", 1), ("q", 63), ("r", 2))            # r ends: its slot and page are free again
+    go(("p", 77), ("q", 1), ("s", 30))           # s takes r's slot
+    go(("p", 1), ("q", 1), ("s", 59))            # q ends (67)
+    go(("p", 1), ("s", 1), ("t", 64))            # p and s end; t fills exactly one page, ends
+    assert at["p"] == 130 and at["s"] == 90
+    go(("u", 2))
+    go(("u", 97))
+    go(("u", 1))
+    assert d.runner.free_token_slots() == 6 * 64 and d.runner.req_to_token_pool.available_size() == 4
+    for k in toks:
+        assert U.rel_err(d.result(k), want[k], dtype) <= TOL[dtype], k
+
+
+def test_window_edge_is_exact_when_one_key_stands_out(tmp_path):
+    """Token 0 is made the one key every later query points at (its latent is copied into the query
+    side by construction of the prompt: all tokens equal), so the step at which it leaves the window
+    changes the output visibly; the engine must follow the plain model through that edge both in a
+    prompt and while decoding."""
+    cfg, w, folder = _model(tmp_path, "a", seed=7, sharp=True)
+    first = 5
+    toks = [first] + [11] * 30                     # identical later tokens: only token 0 differs
+    want = P.forward(cfg, w, toks)
+    # the plain model itself moves at the edge (window 9: position 9 is the first not to see token 0)
+    assert (want[8] - want[12]).abs().max() > 10 * (want[12] - want[13]).abs().max()
+    for dtype in (torch.float32, torch.bfloat16):
+        d = U.Driver(folder, dtype)
+        d.step([("w", toks)], end=["w"])
+        assert U.rel_err(d.result("w"), want, dtype) <= TOL[dtype]
+        d.step([("v", toks[:4])])
+        for t in toks[4:]:
+            d.step([("v", [t])])
+        assert U.rel_err(d.result("v"), want, dtype) <= TOL[dtype]
+
+
+def test_long_decoding_fp32(tmp_path):
+    cfg, w, folder = _model(tmp_path, "c", seed=9)
+    toks = _tokens(cfg, 400, 20)
+    want = P.forward(cfg, w, toks)
+    d = U.Driver(folder, torch.float32)
+    d.step([("r", toks[:1])])
+    for t in toks[1:]:
+        d.step([("r", [t])])
+    assert U.rel_err(d.result("r"), want) <= 1e-4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_engine_and_scheduler(tmp_path, dtype):
+    """Engine.generate: six prompts of unequal length through four request slots with a chunked
+    prefill budget of 48 tokens, so prompts are cut, decodes run beside prompt portions, and slots
+    are reused.  Teacher-forced check of every generated token: the plain model, fed the engine's
+    own continuation, must rank that token first (or within the numeric noise of the top)."""
+    from sglang_security_b200.entrypoints.engine import Engine
+    from sglang_security_b200.managers.schedule_batch import SamplingParams
+
+    cfg, w, folder = _model(tmp_path, "a", seed=11)
+    prompts = [_tokens(cfg, n, 30 + n) for n in (70, 5, 130, 33, 1, 64)]
+    eng = Engine(folder, dtype=dtype, max_total_tokens=8 * 64, max_running_requests=4, chunked_prefill_size=48)
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=12))
+    assert eng.runner.free_token_slots() == 8 * 64
+    margin = 1e-3 if dtype == "float32" else 0.15
+    for p, o in zip(prompts, outs):
+        assert len(o) == 12
+        logits = P.forward(cfg, w, p + o[:-1])
+        for k, tok in enumerate(o):
+            row = logits[len(p) - 1 + k]
+            assert row[tok] >= row.max() - margin * (row.max() - row.min()), (len(p), k)
+    # sampling with a temperature is reproducible under a seed and stays in the vocabulary
+    sp = SamplingParams(max_new_tokens=5, temperature=0.8, top_k=10, top_p=0.9, seed=3)
+    a = eng.generate(prompts[:2], sp)
+    b = eng.generate(prompts[:2], sp)
+    assert a == b and all(0 <= t < cfg["vocab"] for o in a for t in o)
