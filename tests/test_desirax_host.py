@@ -132,10 +132,12 @@ def test_scheduler_chunks_prompts_mixes_decodes_and_respects_slots_and_pages():
 
     run = _FakeRunner(pages=8, slots=2)
     s = Scheduler(run, chunked_prefill_size=100)
-    s.sampler = lambda logits, reqs: [3] * len(reqs)
+    s.sampler = type("S", (), {"__call__": lambda self, logits, reqs: [3] * len(reqs),
+                             "forget": lambda self, rid: None})()
     sp = SamplingParams(max_new_tokens=3)
     for rid, n in (("a", 150), ("b", 30), ("c", 200)):
-        s.add_request(Req(rid=rid, input_ids=[1] * n, sampling_params=sp))
+        s.add_request(Req(rid=rid, input_ids=[1] * n,
+                          sampling_params=SamplingParams(max_new_tokens=8) if rid == "b" else sp))
     done = []
     for _ in range(40):
         done += [r.rid for r in s.step()]
