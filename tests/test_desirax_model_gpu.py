@@ -140,8 +140,13 @@ def test_unequal_requests_in_one_batch_and_reused_pages_and_slots(tmp_path, name
     go(("u", 97))
     go(("u", 1))
     assert d.runner.free_token_slots() == 7 * 64 and d.runner.req_to_token_pool.available_size() == 4
+    alone = U.Driver(folder, dtype, max_tokens=3 * 64, max_requests=1)
     for k in toks:
-        assert U.rel_err(d.result(k), want[k], dtype) <= TOL[dtype], k
+        alone.step([(k, toks[k])], end=[k])
+        # against the same engine running the request alone: reduction order is all that may differ
+        assert U.rel_err(d.result(k), alone.result(k), dtype) <= (1e-5 if dtype == torch.float32 else 3e-2), k
+        # and against the plain model (bf16: top-1 routing among near-equal experts flips often)
+        assert U.rel_err(d.result(k), want[k], dtype) <= (TOL[dtype] if dtype == torch.float32 else 0.12), k
 
 
 def test_window_edge_is_exact_when_one_key_stands_out(tmp_path):
