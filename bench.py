@@ -547,7 +547,19 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debug only)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--arch-compare", default=None, metavar="SIZES",
+                    help="instead of the headline workload: prefill / decode throughput of the Desirax "
+                         "design beside the Llama-family stack at equal size ('all' or comma-separated "
+                         "names of model_executor/arch_bench.py SIZES); one JSON line per model and size")
     args = ap.parse_args()
+    if args.arch_compare:
+        from sglang_security_b200 import build as _build
+        from sglang_security_b200.model_executor import arch_bench
+
+        _build.ensure_built()
+        arch_bench.run(args.steps, max(args.warmup, 3),
+                       None if args.arch_compare == "all" else args.arch_compare.split(","))
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         run_reference(args)

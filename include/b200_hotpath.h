@@ -537,13 +537,19 @@ int b200_latent_prep(const void* qraw, int64_t ldq, int QR, const float* wq, voi
  * tok_b[t] at position p, keys j in [max(0, p - window + 1), p] (window <= 0: [0, p]) found through
  * req_to_token[req_pool[b], j]; score = (q_lat[t,h] . c_j + rotary(q_raw[t,h][q_rot_off:]) . kr_j)
  * * scale, softmax, out[t,h] = sum_j p_j c_j.  fp32 scores / weights / accumulation.  max_keys is a
- * hint (longest key range in the batch, 0 = unknown).                                             */
+ * hint (longest key range in the batch, 0 = unknown).  With ext_start / ext_len (first row and row
+ * count of each of the bs batch entries), 16-bit storage and R, rot multiples of 8, the tensor-core
+ * instance runs (mma.sync, 64 (token, head) rows per CTA); env B200_LATENT_ATTN_MMA=0 keeps the
+ * fp32 CUDA-core instance, which is also the only one for fp32 storage.  num_splits > 1 (tensor-core
+ * instance only) spreads each token's keys over that many CTAs and merges their partial softmaxes
+ * in a second launch; ws must then hold num_splits * T * H * (R + 2) floats.                      */
 int b200_latent_attn(const float* q_lat, int64_t ldql_t, int64_t ldql_h, const void* q_raw,
                      int64_t ldqr_t, int64_t ldqr_h, int q_rot_off, const void* cache, int64_t ldc,
                      const int* r2t, int64_t ld_r2t, const int64_t* req_pool, const int* tok_pos,
-                     const int* tok_b, const float* inv_freq, int rot_dims, int T, int H, int R,
-                     int rot, int window, int max_keys, float scale, void* out, int64_t ldo_t,
-                     int64_t ldo_h, int dtype, void* stream);
+                     const int* tok_b, const int* ext_start, const int* ext_len, int bs,
+                     const float* inv_freq, int rot_dims, int T, int H, int R, int rot, int window,
+                     int max_keys, float scale, void* out, int64_t ldo_t, int64_t ldo_h, int num_splits,
+                     float* ws, int64_t ws_floats, int dtype, void* stream);
 /* Router: z = wr h + br (fp32), the `top` largest logits (ties: lowest index), weights = softmax
  * over the chosen logits; gate[t] = sigmoid(wsg . h) when wsg is given.                           */
 int b200_moe_route(const void* h, int64_t ldh, const float* wr, const float* br, int E, int W,

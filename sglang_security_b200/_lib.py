@@ -163,8 +163,9 @@ _SIGNATURES = {
                                  c_void_p, c_int64, c_float, c_int, c_int, c_void_p]),
     "b200_latent_attn": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int,
                                  c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
-                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                 c_void_p, c_int64, c_int64, c_int, c_void_p]),
+                                 c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                 c_int, c_int, c_float, c_void_p, c_int64, c_int64, c_int, c_void_p,
+                                 c_int64, c_int, c_void_p]),
     "b200_moe_route": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "b200_moe_align": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),

@@ -12,6 +12,9 @@
 //                 the KV latent and interleaved rotary embedding of the shared key part, written
 //                 straight into the token's pool row.
 #include "common.cuh"
+#include "latent_attn_mma.cuh"
+
+#include <cstdlib>
 
 namespace b200 {
 
@@ -288,6 +291,41 @@ static int latent_attn_dispatch(int T_tokens, int max_keys, cudaStream_t st, con
 #undef GO
 }
 
+template <typename T, int CW>
+static int latent_attn_mma_launch(int grid_x, int grid_y, size_t smem, cudaStream_t st, const float* q_lat,
+                                  int64_t ldql_t, int64_t ldql_h, const void* q_raw, int64_t ldqr_t,
+                                  int64_t ldqr_h, int q_rot_off, const void* cache, int64_t ldc,
+                                  const int* r2t, int64_t ld_r2t, const int64_t* req_pool,
+                                  const int* tok_pos, const int* ext_start, const int* ext_len, int bs,
+                                  const float* inv_freq, int rot_dims, int H, int HG, int TQ, int R,
+                                  int rot, int window, float scale, void* out, int64_t ldo_t,
+                                  int64_t ldo_h, int nsplit, float* ws) {
+  auto kern = latent_attn_mma_kernel<T, CW>;
+  if (smem > 48 * 1024)
+    B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(smem)));
+  launch_kernel(kern, dim3(grid_x, grid_y, nsplit), dim3(kLaThreads), smem, st, 1, 0, q_lat, ldql_t, ldql_h,
+                static_cast<const T*>(q_raw), ldqr_t, ldqr_h, q_rot_off, static_cast<const T*>(cache),
+                ldc, r2t, ld_r2t, req_pool, tok_pos, ext_start, ext_len, bs, inv_freq, rot_dims, H, HG,
+                TQ, R, rot, window, scale, static_cast<T*>(out), ldo_t, ldo_h, nsplit, ws, grid_x);
+  B200_CHECK_LAUNCH("latent_attn_mma_kernel");
+  if (nsplit > 1) {
+    launch_kernel(latent_attn_merge_kernel<T>, dim3(grid_x * H), dim3(128), 0, st, 1, 0,
+                  static_cast<const float*>(ws), nsplit, grid_x, H, R, static_cast<T*>(out), ldo_t, ldo_h);
+    B200_CHECK_LAUNCH("latent_attn_merge_kernel");
+  }
+  note_variant("latent_attn_mma cw%d hg%d tq%d smem%zu splits%d", CW, HG, TQ, smem, nsplit);
+  return 0;
+}
+
+static bool latent_attn_mma_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("B200_LATENT_ATTN_MMA");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 }  // namespace b200
 
 extern "C" int b200_latent_prep(const void* qraw, int64_t ldq, int QR, const float* wq, void* cq,
@@ -303,6 +341,7 @@ extern "C" int b200_latent_prep(const void* qraw, int64_t ldq, int QR, const flo
                           rot_dims % 2 == 0 && (rot_dims == 0 || inv_freq)),
                "b200_latent_prep: KV latent arguments");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer("latent_prep", st);
 #define LAUNCH(TT)                                                                                   \
   launch_kernel(latent_prep_kernel<TT>, dim3(T), dim3(kPrepThreads), 0, st, 1, 0,                    \
                 static_cast<const TT*>(qraw), ldq, QR, wq, static_cast<TT*>(cq), ldcq,               \
@@ -320,10 +359,11 @@ extern "C" int b200_latent_prep(const void* qraw, int64_t ldq, int QR, const flo
 extern "C" int b200_latent_attn(const float* q_lat, int64_t ldql_t, int64_t ldql_h, const void* q_raw,
                                 int64_t ldqr_t, int64_t ldqr_h, int q_rot_off, const void* cache,
                                 int64_t ldc, const int* r2t, int64_t ld_r2t, const int64_t* req_pool,
-                                const int* tok_pos, const int* tok_b, const float* inv_freq,
-                                int rot_dims, int T, int H, int R, int rot, int window, int max_keys,
-                                float scale, void* out, int64_t ldo_t, int64_t ldo_h, int dtype,
-                                void* stream) {
+                                const int* tok_pos, const int* tok_b, const int* ext_start,
+                                const int* ext_len, int bs, const float* inv_freq, int rot_dims, int T,
+                                int H, int R, int rot, int window, int max_keys, float scale, void* out,
+                                int64_t ldo_t, int64_t ldo_h, int num_splits, float* ws,
+                                int64_t ws_floats, int dtype, void* stream) {
   using namespace b200;
   if (T == 0) return 0;
   B200_REQUIRE(q_lat && cache && r2t && req_pool && tok_pos && tok_b && out,
@@ -332,8 +372,38 @@ extern "C" int b200_latent_attn(const float* q_lat, int64_t ldql_t, int64_t ldql
                    rot_dims % 2 == 0 && (rot_dims == 0 || inv_freq),
                "b200_latent_attn: bad sizes (H %d R %d rot %d rot_dims %d)", H, R, rot, rot_dims);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer("latent_attn", st);
   if (max_keys <= 0) max_keys = 1 << 30;
   if (window > 0) max_keys = min(max_keys, window);
+  // 16-bit storage with 16-byte-copyable rows: the tensor-core instance
+  const int R16 = (R + 15) & ~15, rot16 = (rot + 15) & ~15;
+  if ((dtype == B200_BF16 || dtype == B200_F16) && latent_attn_mma_enabled() && ext_start && ext_len &&
+      bs > 0 && R % 8 == 0 && rot % 8 == 0 && ldc % 8 == 0 && aligned16(cache) && R16 <= 512) {
+    const int HG = min(H, kLaRows), TQ = kLaRows / HG;
+    const size_t smem = static_cast<size_t>(kLaRows + 2 * kLaKeys) * (R16 + rot16 + 8) * 2;
+    const int gy = ceil_div(H, HG);
+    int nsplit = max(1, num_splits);
+    if (nsplit > 1)
+      B200_REQUIRE(ws && ws_floats >= static_cast<int64_t>(nsplit) * T * H * (R + 2),
+                   "b200_latent_attn: workspace too small for %d splits", nsplit);
+#define GO_MMA(TT, CW)                                                                               \
+  return latent_attn_mma_launch<TT, CW>(T, gy, smem, st, q_lat, ldql_t, ldql_h, q_raw, ldqr_t, ldqr_h, \
+                                        q_rot_off, cache, ldc, r2t, ld_r2t, req_pool, tok_pos,        \
+                                        ext_start, ext_len, bs, inv_freq, rot_dims, H, HG, TQ, R, rot, \
+                                        window, scale, out, ldo_t, ldo_h, nsplit, ws)
+#define BY_CW(TT)                      \
+  do {                                 \
+    if (R16 <= 32) GO_MMA(TT, 16);     \
+    if (R16 <= 64) GO_MMA(TT, 32);     \
+    if (R16 <= 128) GO_MMA(TT, 64);    \
+    if (R16 <= 256) GO_MMA(TT, 128);   \
+    GO_MMA(TT, 256);                   \
+  } while (0)
+    if (dtype == B200_BF16) BY_CW(__nv_bfloat16);
+    BY_CW(__half);
+#undef BY_CW
+#undef GO_MMA
+  }
 #define GO(TT)                                                                                       \
   return latent_attn_dispatch<TT>(T, max_keys, st, q_lat, ldql_t, ldql_h, q_raw, ldqr_t, ldqr_h,     \
                                   q_rot_off, cache, ldc, r2t, ld_r2t, req_pool, tok_pos, tok_b,      \

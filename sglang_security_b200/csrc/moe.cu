@@ -10,41 +10,45 @@
 //                      act(gate) * up is stored in sorted order; otherwise A is that intermediate and
 //                      the result is scattered back to row t * top + k for the weighted combine.
 #include "common.cuh"
+#include "latent_attn_mma.cuh"   // ldmatrix / mma.sync wrappers
 
 namespace b200 {
 
 constexpr int kMaxExpertsPerLane = 8;  // experts <= 256
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ h, int64_t ldh, const float* __restrict__ wr,
                  const float* __restrict__ br, int E, int W, int top, const float* __restrict__ wsg,
                  int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ gate, int Tn) {
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (t >= Tn) return;
+  // one CTA per token: its 8 warps share the experts' dot products (and the gate's), warp 0 ranks
+  __shared__ float z_s[32 * kMaxExpertsPerLane];
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T* row = h + t * ldh;
+  const int jobs = E + ((wsg && gate) ? 1 : 0);
+  for (int e = warp; e < jobs; e += 8) {
+    const float* w = e < E ? wr + static_cast<int64_t>(e) * W : wsg;
+    float s0 = 0.f, s1 = 0.f;
+    int d = lane;
+    for (; d + 32 < W; d += 64) {
+      s0 = fmaf(w[d], to_float<T>(row[d]), s0);
+      s1 = fmaf(w[d + 32], to_float<T>(row[d + 32]), s1);
+    }
+    if (d < W) s0 = fmaf(w[d], to_float<T>(row[d]), s0);
+    float s = s0 + s1;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) {
+      if (e < E) z_s[e] = s + (br ? br[e] : 0.f);
+      else gate[t] = 1.0f / (1.0f + expf(-s));
+    }
+  }
+  __syncthreads();
+  if (warp != 0) return;
   float z[kMaxExpertsPerLane];
 #pragma unroll
-  for (int i = 0; i < kMaxExpertsPerLane; ++i) z[i] = -INFINITY;
-  for (int e = 0; e < E; ++e) {
-    const float* w = wr + static_cast<int64_t>(e) * W;
-    float s = 0.f;
-    for (int d = lane; d < W; d += 32) s = fmaf(w[d], to_float<T>(row[d]), s);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    s += br ? br[e] : 0.f;
-#pragma unroll
-    for (int i = 0; i < kMaxExpertsPerLane; ++i)
-      if (e == lane + 32 * i) z[i] = s;
-  }
-  if (wsg && gate) {
-    float s = 0.f;
-    for (int d = lane; d < W; d += 32) s = fmaf(wsg[d], to_float<T>(row[d]), s);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane == 0) gate[t] = 1.0f / (1.0f + expf(-s));
-  }
+  for (int i = 0; i < kMaxExpertsPerLane; ++i) z[i] = (lane + 32 * i < E) ? z_s[lane + 32 * i] : -INFINITY;
   float zmax = 0.f, sum = 0.f, mine = 0.f;  // lane k keeps the k-th chosen logit
   for (int k = 0; k < top; ++k) {
     float bv = -INFINITY;
@@ -195,6 +199,114 @@ moe_grouped_gemm_kernel(const T* __restrict__ a, int64_t lda, const T* __restric
   }
 }
 
+// Tensor-core instance for 16-bit types (K a multiple of 8, 16-byte aligned rows): 64 sorted rows of
+// one expert x 64 output columns (gated: 64 gate + the 64 matching up columns) per CTA, K in steps of
+// 64 through a cp.async double buffer, 4 warps x (16 rows x 64 columns) of mma.sync m16n8k16, fp32
+// accumulation; the gated epilogue applies act(gate) * up on the fp32 accumulators.
+constexpr int kTM = 64, kTN = 64, kTK = 64, kTLd = kTK + 8;
+
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(128)
+moe_grouped_gemm_mma_kernel(const T* __restrict__ a, int64_t lda, const T* __restrict__ w, int64_t ldw,
+                            int64_t w_expert_stride, const int* __restrict__ offsets,
+                            const int* __restrict__ sorted_rows, int E, int top, int Nout, int K,
+                            T* __restrict__ out, int64_t ldo, int act) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int NB = GATED ? 2 * kTN : kTN;
+  T* As = reinterpret_cast<T*>(smem_raw);            // [2][kTM][kTLd]
+  T* Bs = As + 2 * kTM * kTLd;                       // [2][NB][kTLd]
+  __shared__ int rows[kTM];
+  int e = 0, tile = blockIdx.x, lo = 0, hi = 0;
+  for (; e < E; ++e) {
+    lo = offsets[e];
+    hi = offsets[e + 1];
+    const int nt = (hi - lo + kTM - 1) / kTM;
+    if (tile < nt) break;
+    tile -= nt;
+  }
+  if (e >= E) return;
+  const int m0 = lo + tile * kTM, mcount = min(kTM, hi - m0);
+  const int n0 = blockIdx.y * kTN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < kTM) rows[tid] = tid < mcount ? sorted_rows[m0 + tid] : -1;
+  __syncthreads();
+  const T* we = w + e * w_expert_stride;
+  auto load_tile = [&](int k0, int buf) {
+    T* ad = As + buf * kTM * kTLd;
+    for (int c = tid; c < kTM * (kTK / 8); c += 128) {
+      const int r = c >> 3, ch = c & 7;
+      T* d = ad + r * kTLd + ch * 8;
+      if (r < mcount && k0 + ch * 8 < K) {
+        const int64_t src = GATED ? rows[r] / top : m0 + r;
+        cp_async16(smem_u32(d), a + src * lda + k0 + ch * 8);
+      } else {
+        *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    T* bd = Bs + buf * NB * kTLd;
+    for (int c = tid; c < NB * (kTK / 8); c += 128) {
+      const int r = c >> 3, ch = c & 7;
+      const int half = r / kTN, n = n0 + (r - half * kTN);
+      T* d = bd + r * kTLd + ch * 8;
+      if (n < Nout && k0 + ch * 8 < K)
+        cp_async16(smem_u32(d), we + (static_cast<int64_t>(half) * Nout + n) * ldw + k0 + ch * 8);
+      else
+        *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+    }
+    cp_async_commit();
+  };
+  float acc[8][4], acc2[GATED ? 8 : 1][4];
+#pragma unroll
+  for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+#pragma unroll
+  for (int n = 0; n < (GATED ? 8 : 1); ++n) acc2[n][0] = acc2[n][1] = acc2[n][2] = acc2[n][3] = 0.f;
+  const int nk = (K + kTK - 1) / kTK;
+  load_tile(0, 0);
+  for (int kt = 0; kt < nk; ++kt) {
+    cp_async_wait<0>();
+    __syncthreads();
+    if (kt + 1 < nk) load_tile((kt + 1) * kTK, (kt + 1) & 1);
+    const T* at = As + (kt & 1) * kTM * kTLd;
+    const T* bt = Bs + (kt & 1) * NB * kTLd;
+    const uint32_t a_base = smem_u32(at + (warp * 16 + (lane & 15)) * kTLd + (lane >> 4) * 8);
+    const uint32_t b_base = smem_u32(bt + ((lane & 7) + ((lane >> 4) << 3)) * kTLd + ((lane >> 3) & 1) * 8);
+#pragma unroll
+    for (int ks = 0; ks < kTK; ks += 16) {
+      uint32_t af[4];
+      ldsm_x4(af[0], af[1], af[2], af[3], a_base + ks * 2);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(b0, b1, b2, b3, b_base + (np * 16 * kTLd + ks) * 2);
+        mma16816<T>(acc[2 * np], af, b0, b1);
+        mma16816<T>(acc[2 * np + 1], af, b2, b3);
+        if (GATED) {
+          ldsm_x4(b0, b1, b2, b3, b_base + ((kTN + np * 16) * kTLd + ks) * 2);
+          mma16816<T>(acc2[GATED ? 2 * np : 0], af, b0, b1);
+          mma16816<T>(acc2[GATED ? 2 * np + 1 : 0], af, b2, b3);
+        }
+      }
+    }
+  }
+  const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int lr = warp * 16 + g + 8 * i;
+    if (lr >= mcount) continue;
+    const int64_t orow = GATED ? m0 + lr : rows[lr];
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int col = n0 + n * 8 + 2 * t4 + c;
+        if (col >= Nout) continue;
+        const float v = GATED ? moe_act(acc[n][2 * i + c], act) * acc2[GATED ? n : 0][2 * i + c]
+                              : acc[n][2 * i + c];
+        out[orow * ldo + col] = from_float<T>(v);
+      }
+  }
+}
+
 }  // namespace b200
 
 extern "C" int b200_moe_route(const void* h, int64_t ldh, const float* wr, const float* br, int E,
@@ -206,9 +318,10 @@ extern "C" int b200_moe_route(const void* h, int64_t ldh, const float* wr, const
   B200_REQUIRE(E > 0 && E <= 32 * kMaxExpertsPerLane && top > 0 && top <= E && top <= 32 && W > 0,
                "b200_moe_route: experts %d (max %d), top %d", E, 32 * kMaxExpertsPerLane, top);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const dim3 grid(ceil_div(T, 4));
+  ScopedKernelTimer timer("moe_route", st);
+  const dim3 grid(T);
 #define LAUNCH(TT)                                                                                   \
-  launch_kernel(moe_route_kernel<TT>, grid, dim3(128), 0, st, 1, 0, static_cast<const TT*>(h), ldh,  \
+  launch_kernel(moe_route_kernel<TT>, grid, dim3(256), 0, st, 1, 0, static_cast<const TT*>(h), ldh,  \
                 wr, br, E, W, top, wsg, ids, wts, gate, T)
   if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
   else if (dtype == B200_F16) LAUNCH(__half);
@@ -224,6 +337,7 @@ extern "C" int b200_moe_align(const int* ids, int N, int E, int* offsets, int* s
   using namespace b200;
   B200_REQUIRE(ids && offsets && sorted_rows && N >= 0 && E > 0 && E <= 4096, "b200_moe_align: bad arguments");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer("moe_align", st);
   launch_kernel(moe_align_kernel, dim3(1), dim3(1024), static_cast<size_t>(E + 1) * 4, st, 1, 0, ids,
                 N, E, offsets, sorted_rows);
   B200_CHECK_LAUNCH("moe_align_kernel");
@@ -241,6 +355,33 @@ extern "C" int b200_moe_grouped_gemm(const void* a, int64_t lda, const void* w, 
   B200_REQUIRE(E > 0 && top > 0 && rows > 0 && Nout > 0 && K > 0 && (act == 0 || act == 1),
                "b200_moe_grouped_gemm: bad sizes");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer("moe_grouped_gemm", st);
+  if ((dtype == B200_BF16 || dtype == B200_F16) && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 &&
+      w_expert_stride % 8 == 0 && aligned16(a) && aligned16(w)) {
+    const dim3 tgrid(ceil_div(rows, kTM) + min(E, rows), ceil_div(Nout, kTN));
+    const size_t smem = static_cast<size_t>(2 * kTM + 2 * (gated ? 2 : 1) * kTN) * kTLd * 2;
+#define LAUNCH_TC(TT, G)                                                                             \
+  do {                                                                                               \
+    auto kern = moe_grouped_gemm_mma_kernel<TT, G>;                                                  \
+    if (smem > 48 * 1024)                                                                            \
+      B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,           \
+                                        static_cast<int>(smem)));                                    \
+    launch_kernel(kern, tgrid, dim3(128), smem, st, 1, 0, static_cast<const TT*>(a), lda,            \
+                  static_cast<const TT*>(w), ldw, w_expert_stride, offsets, sorted_rows, E, top,     \
+                  Nout, K, static_cast<TT*>(out), ldo, act);                                         \
+  } while (0)
+    if (dtype == B200_BF16) {
+      if (gated) LAUNCH_TC(__nv_bfloat16, true);
+      else LAUNCH_TC(__nv_bfloat16, false);
+    } else {
+      if (gated) LAUNCH_TC(__half, true);
+      else LAUNCH_TC(__half, false);
+    }
+#undef LAUNCH_TC
+    B200_CHECK_LAUNCH("moe_grouped_gemm_mma_kernel");
+    note_variant("moe_grouped_gemm_mma gated%d", gated);
+    return 0;
+  }
   // every expert can leave one partly filled row tile
   const dim3 grid(ceil_div(rows, kGM) + min(E, rows), ceil_div(Nout, kGN));
 #define LAUNCH(TT, G)                                                                                \

@@ -142,6 +142,7 @@ extern "C" int b200_scalar_rmsnorm_shift(const float* x, int64_t ldx, const floa
   B200_REQUIRE(mu || out_h, "b200_scalar_rmsnorm_shift: out_h is NULL");
   B200_REQUIRE(!state || slot, "b200_scalar_rmsnorm_shift: state without slots");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer("scalar_rmsnorm_shift", st);
 #define LAUNCH(TO)                                                                                   \
   launch_kernel(scalar_rmsnorm_shift_kernel<TO>, dim3(T), dim3(kRowThreads), 0, st, 1, 0, x, ldx,   \
                 gain, weight, eps, mu, state, ld_state, tok_pos, tok_b, ext_start, ext_len, slot,    \
@@ -164,6 +165,7 @@ extern "C" int b200_residual_combine(float* x, int64_t ldx, const void* a, int64
   B200_REQUIRE(x && T > 0 && W > 0, "b200_residual_combine: bad arguments");
   B200_REQUIRE(!y || (topk_w && top > 0), "b200_residual_combine: expert rows without weights");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer("residual_combine", st);
 #define LAUNCH(TA)                                                                                   \
   launch_kernel(residual_combine_kernel<TA>, dim3(T), dim3(kRowThreads), 0, st, 1, 0, x, ldx,       \
                 static_cast<const TA*>(a), lda, static_cast<const TA*>(b), ldb,                      \
@@ -183,6 +185,7 @@ extern "C" int b200_act_and_mul(const void* z, int64_t ldz, void* out, int64_t l
   if (T == 0) return 0;
   B200_REQUIRE(z && out && T > 0 && D > 0 && (kind == 0 || kind == 1), "b200_act_and_mul: bad arguments");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer("act_and_mul", st);
 #define LAUNCH(TT)                                                                                   \
   launch_kernel(act_and_mul_kernel<TT>, dim3(T), dim3(kRowThreads), 0, st, 1, 0,                    \
                 static_cast<const TT*>(z), ldz, static_cast<TT*>(out), ldo, D, kind)

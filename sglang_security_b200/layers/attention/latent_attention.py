@@ -24,6 +24,9 @@ from ..linear import ColumnParallelLinear, RowParallelLinear
 from ..rotary_embedding import InterleavedRotary
 
 
+_SM_COUNT = 148      # B200
+
+
 def _bmm_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """Batched product with a fp32 result (16-bit operands keep their tensor-core path)."""
     if a.dtype == torch.float32:
@@ -92,13 +95,23 @@ class LatentAttention(nn.Module):
         q3 = q.view(t, self.heads, self.dim + self.rot_dim)
         q_lat = _bmm_f32(q3[:, :, :self.dim].transpose(0, 1), self.w_uk)           # [H, T, R] fp32
         o_lat = torch.empty((self.heads, t, self.kv_rank), dtype=h.dtype, device=h.device)
+        # few tokens with many keys each (decoding): spread every token's keys over several CTAs
+        keys = min(self.window, int(fb.max_seq_len)) if self.window else int(fb.max_seq_len)
+        ctas = t * ((self.heads + 63) // 64)
+        splits = 1
+        if h.dtype != torch.float32 and ctas < _SM_COUNT and keys > 128:
+            splits = max(1, min((keys + 63) // 64, (2 * _SM_COUNT) // ctas, 64))
+        ws = (torch.empty(splits * t * self.heads * (self.kv_rank + 2), dtype=torch.float32, device=h.device)
+              if splits > 1 else None)
         rc = lib.b200_latent_attn(
             q_lat.data_ptr(), q_lat.stride(1), q_lat.stride(0), q.data_ptr(), q3.stride(0), q3.stride(1),
             self.dim, cache.data_ptr(), cache.stride(0), fb.req_to_token_pool.req_to_token.data_ptr(),
             fb.req_to_token_pool.req_to_token.stride(0), fb.req_pool_indices.data_ptr(),
-            fb.tok_pos.data_ptr(), fb.tok_b.data_ptr(), _lib.ptr(inv_freq), self.rotary.dims, t,
+            fb.tok_pos.data_ptr(), fb.tok_b.data_ptr(), fb.ext_start.data_ptr(), fb.ext_len.data_ptr(),
+            fb.batch_size, _lib.ptr(inv_freq), self.rotary.dims, t,
             self.heads, self.kv_rank, self.rot_dim, self.window, int(fb.max_seq_len), self.scale,
-            o_lat.data_ptr(), o_lat.stride(1), o_lat.stride(0), code, _lib.current_stream())
+            o_lat.data_ptr(), o_lat.stride(1), o_lat.stride(0), splits, _lib.ptr(ws),
+            ws.numel() if ws is not None else 0, code, _lib.current_stream())
         _lib.check(rc, "b200_latent_attn")
         v = torch.bmm(o_lat, self.w_uv_t)                                          # [H, T, vdim]
         out, _ = self.o_proj(v.transpose(0, 1).reshape(t, self.heads * self.vdim))

@@ -1,0 +1,218 @@
+"""Prefill and decode throughput of the Desirax design at layer sizes that resemble a real model's,
+beside the Llama-family decoder stack of this package at equal width / heads / head size / layer count
+and equal active feed-forward size (random weights, bf16).  Driven by `bench.py --arch-compare`.
+
+Timing: CUDA events on the launching stream around whole engine steps, after warm-up steps; every step
+touches more weight and cache bytes than L2 holds at the larger size.  Per-kernel times come from the
+library's timing registry (events around each launch) in a separate pass."""
+from __future__ import annotations
+
+import json
+import statistics
+import time
+from types import SimpleNamespace
+
+import torch
+
+from .. import _lib
+
+SIZES = {
+    # dense feed-forward everywhere: the direct counterpart of a Llama layer
+    "w1024-dense": dict(width=1024, heads=8, dim=64, rot=64, vdim=128, kv_rank=256, q_rank=384, window=1024,
+                        layers=4, ff=4096, moe=None, vocab=32000),
+    # mixture of experts with a shared expert; active feed-forward 4 * 1024 + 1024
+    "w2048-moe": dict(width=2048, heads=16, dim=64, rot=64, vdim=128, kv_rank=512, q_rank=768, window=4096,
+                      layers=4, ff=5120, moe=dict(experts=32, top=4, ff=1024, shared=1024), vocab=32000),
+}
+WORK = dict(prefill_reqs=4, prefill_len=2048, decode_bs=32, decode_ctx=2048)
+
+
+def _desirax_cfg(s):
+    m = {"dim": s["dim"], "heads": s["heads"], "kv_rank": s["kv_rank"], "q_rank": s["q_rank"],
+         "rot_dim": s["rot"], "vdim": s["vdim"], "rot": {"base": 1e6, "dims": s["rot"]},
+         "scale": (s["dim"] + s["rot"]) ** -0.5, "mask": {"size": s["window"]}}
+    if s["moe"]:
+        f = {"kind": "moe", "router": {"experts": s["moe"]["experts"], "top": s["moe"]["top"]},
+             "expert": {"ff": s["moe"]["ff"]}, "shared": {"ff": s["moe"]["shared"]}}
+    else:
+        f = {"kind": "dense", "ff": s["ff"]}
+    return {"architecture": "Desirax", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5},
+            "layers": [{"type": "latent_attention", "mixer": dict(m), "mlp": f} for _ in range(s["layers"])]}
+
+
+def _timed(fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ms = []
+    for _ in range(steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms.append(e0.elapsed_time(e1))
+    return statistics.median(ms)
+
+
+def _kernel_times(fn, names):
+    _lib.timing_enable(True)
+    _lib.timing_read("")
+    fn()
+    torch.cuda.synchronize()
+    out = {}
+    for n in names:
+        k, ms = _lib.timing_read(n)
+        if k:
+            out[n] = {"launches": k, "ms": round(ms, 4)}
+    _lib.timing_enable(False)
+    _lib.timing_read("")
+    return out
+
+
+def bench_desirax(name, s, steps, warmup, device="cuda"):
+    from ..configs.desirax import desirax_config
+    from ..managers.schedule_batch import Req, StepItem
+    from ..managers.scheduler import Scheduler
+    from ..models.registry import resolve_model_cls
+    from .model_runner import ModelRunner
+
+    cfg = desirax_config(_desirax_cfg(s))
+    torch.manual_seed(0)
+    with torch.device(device):
+        model = resolve_model_cls("Desirax")(cfg, params_dtype=torch.bfloat16)
+    for n_, p in model.named_parameters():
+        if p.dim() == 0:
+            p.data.fill_(1.0)
+        elif n_.endswith("mu"):
+            p.data.uniform_(0, 1)
+        elif "norm_weight" in n_:
+            p.data.fill_(1.0)
+        else:
+            p.data.normal_(0, 0.02)
+    W = WORK
+    bs = max(W["prefill_reqs"], W["decode_bs"])
+    tokens = W["decode_bs"] * (W["decode_ctx"] + 64) + W["prefill_reqs"] * W["prefill_len"]
+    runner = ModelRunner(None, torch.bfloat16, max_total_tokens=tokens, max_running_requests=bs,
+                         context_length=max(W["prefill_len"], W["decode_ctx"] + 64), device=device,
+                         model=model.eval(), model_config=SimpleNamespace(architecture="Desirax", hf_config=cfg))
+    sched = Scheduler(runner)
+    g = torch.Generator().manual_seed(1)
+    rnd = lambda n: torch.randint(0, s["vocab"], (n,), generator=g).tolist()
+
+    def prefill():
+        reqs = [Req(rid=f"p{i}", input_ids=rnd(W["prefill_len"])) for i in range(W["prefill_reqs"])]
+        for r in reqs:
+            assert runner.admit(r)
+        sched.run_step([StepItem(r, r.input_ids, want=[len(r.input_ids) - 1]) for r in reqs])
+        for r in reqs:
+            runner.release(r)
+
+    row = {"arch": "desirax", "size": name}
+    ms = _timed(prefill, steps, warmup)
+    ntok = W["prefill_reqs"] * W["prefill_len"]
+    row["prefill_ms"], row["prefill_tokens_per_s"] = round(ms, 3), round(ntok / ms * 1e3)
+    attn_names = ["latent_attn", "latent_prep", "moe_grouped_gemm", "moe_route", "moe_align",
+                  "scalar_rmsnorm_shift", "residual_combine", "act_and_mul"]
+    row["prefill_kernels"] = _kernel_times(prefill, attn_names)
+    # decode: bs requests at the decode context
+    reqs = [Req(rid=f"d{i}", input_ids=rnd(W["decode_ctx"])) for i in range(W["decode_bs"])]
+    for r in reqs:
+        assert runner.admit(r)
+    for i in range(0, len(reqs), 4):
+        sched.run_step([StepItem(r, r.input_ids) for r in reqs[i:i + 4]])
+    state = {"n": 0}
+
+    def decode():
+        state["n"] += 1
+        assert state["n"] < 60
+        sched.run_step([StepItem(r, [7], want=[0]) for r in reqs])
+
+    ms = _timed(decode, steps, warmup)
+    row["decode_ms"], row["decode_tokens_per_s"] = round(ms, 3), round(W["decode_bs"] / ms * 1e3)
+    row["decode_kernels"] = _kernel_times(decode, attn_names)
+    H, R, rot, Wn = s["heads"], s["kv_rank"], s["rot"], min(s["window"], W["prefill_len"])
+    # latent attention, algorithmic work of one launch (all tokens, one layer)
+    keys_prefill = sum(min(p + 1, s["window"]) for p in range(W["prefill_len"])) * W["prefill_reqs"]
+    row["latent_attn_prefill_flops"] = 2 * keys_prefill * H * (2 * R + rot)
+    keys_decode = W["decode_bs"] * min(W["decode_ctx"] + 1, s["window"])
+    row["latent_attn_decode_bytes"] = keys_decode * (R + rot) * 2
+    row["latent_attn_decode_flops"] = 2 * keys_decode * H * (2 * R + rot)
+    del runner, sched, model
+    torch.cuda.empty_cache()
+    return row
+
+
+def bench_llama_like(name, s, steps, warmup, device="cuda"):
+    """The package's Llama-family stack (B200DecoderLayer: fused RMSNorm, rotary + KV write, paged
+    attention, gated silu MLP) at the same width, heads, head size 128, layers, GQA 4:1, bf16."""
+    from .decode_step import B200DecodeStep, ModelGeometry
+    from .forward_batch_info import ForwardBatch, ForwardMode
+
+    W = WORK
+    hd = s["dim"] + s["rot"]
+    geo = ModelGeometry(name, s["width"], s["heads"], max(1, s["heads"] // 4), hd, s["ff"], s["layers"],
+                        s["vocab"], 1e6, False)
+    bs = W["decode_bs"]
+    ctx_cap = max(W["prefill_len"], W["decode_ctx"] + 64)
+    model = B200DecodeStep(geo, None, device, max_bs=bs, max_ctx=ctx_cap, fill_kv=True)
+    dev = device
+    rows = torch.arange(bs, device=dev)
+    model.req_to_token_pool.req_to_token[:bs, :ctx_cap] = (
+        1 + rows[:, None] * ctx_cap + torch.arange(ctx_cap, device=dev)[None]).to(torch.int32)
+    U, L = W["prefill_reqs"], W["prefill_len"]
+    ids = torch.randint(0, s["vocab"], (U * L,), device=dev)
+    pos = torch.arange(L, device=dev).repeat(U)
+    ext = torch.full((U,), L, dtype=torch.int32)
+    pre = torch.zeros(U, dtype=torch.int32)
+    start = torch.arange(U, dtype=torch.int32) * L
+    loc = model.req_to_token_pool.req_to_token[:U, :L].reshape(-1).to(torch.int64)
+    fb = ForwardBatch(forward_mode=ForwardMode.EXTEND, batch_size=U,
+                      req_pool_indices=torch.arange(U, dtype=torch.int64, device=dev),
+                      seq_lens=ext.to(torch.int64).to(dev), out_cache_loc=loc, seq_lens_sum=U * L,
+                      seq_lens_cpu=ext.to(torch.int64), extend_seq_lens=ext.to(dev), extend_prefix_lens=pre.to(dev),
+                      extend_start_loc=start.to(dev), extend_seq_lens_cpu=[L] * U, extend_prefix_lens_cpu=[0] * U,
+                      extend_num_tokens=U * L, req_to_token_pool=model.req_to_token_pool,
+                      token_to_kv_pool=model.token_to_kv_pool, attn_backend=model.attn_backend)
+    last = (start + ext - 1).to(torch.int64).to(dev)
+    out = torch.empty((U,), dtype=torch.int64, device=dev)
+    model.attn_backend.init_forward_metadata(fb)
+    row = {"arch": "llama-like", "size": name}
+    prefill = lambda: model.forward_extend(ids, pos, fb, last, out)
+    ms = _timed(prefill, steps, warmup)
+    row["prefill_ms"], row["prefill_tokens_per_s"] = round(ms, 3), round(U * L / ms * 1e3)
+    names = ["attn_extend", "attn_decode_split", "attn_decode", "attn_merge", "rmsnorm", "silu_and_mul", "rope_kv_write"]
+    row["prefill_kernels"] = _kernel_times(prefill, names)
+    p = W["decode_ctx"]
+    d_len = torch.full((bs,), p + 1, dtype=torch.int64, device=dev)
+    d_loc = model.req_to_token_pool.req_to_token[:bs, p].to(torch.int64)
+    fbd = model.make_forward_batch(bs, torch.arange(bs, dtype=torch.int64, device=dev), d_len, d_loc, bs * (p + 1))
+    model.attn_backend.init_forward_metadata(fbd)
+    d_ids = torch.randint(0, s["vocab"], (bs,), device=dev)
+    d_pos = torch.full((bs,), p, dtype=torch.int64, device=dev)
+    d_out = torch.empty((bs,), dtype=torch.int64, device=dev)
+    decode = lambda: model.forward(d_ids, d_pos, fbd, d_out)
+    ms = _timed(decode, steps, warmup)
+    row["decode_ms"], row["decode_tokens_per_s"] = round(ms, 3), round(bs / ms * 1e3)
+    row["decode_kernels"] = _kernel_times(decode, names)
+    hkv = max(1, s["heads"] // 4)
+    row["attn_prefill_flops"] = 4 * U * (L * (L + 1) // 2) * s["heads"] * hd
+    row["attn_decode_bytes"] = bs * (p + 1) * hkv * hd * 2 * 2
+    del model
+    torch.cuda.empty_cache()
+    return row
+
+
+def run(steps: int, warmup: int, sizes=None):
+    rows = []
+    for name, s in SIZES.items():
+        if sizes and name not in sizes:
+            continue
+        for fn in (bench_desirax, bench_llama_like):
+            t0 = time.time()
+            row = fn(name, s, steps, warmup)
+            row["wall_s"] = round(time.time() - t0, 1)
+            row["workload"] = WORK
+            print(json.dumps(row), flush=True)
+            rows.append(row)
+    return rows

@@ -186,7 +186,8 @@ def _attn_setup(m, width, dtype, seed):
 def test_latent_attention_portions_against_whole_sequence(dtype, geom):
     """Portions of unequal size (two requests side by side, one also decoded token by token) against
     the plain attention over the whole sequence: window edges, 32-key tile edges and page edges are
-    all crossed."""
+    all crossed; the single tokens of the long request see more than 128 keys where there is no
+    window, which is where the 16-bit path spreads a token's keys over several CTAs."""
     import desirax_util as U
     from sglang_security_b200.managers.schedule_batch import Req, StepItem, prepare
     from sglang_security_b200.mem_cache.latent_pool import LatentTokenToKVPool, SeqStatePool
@@ -196,7 +197,7 @@ def test_latent_attention_portions_against_whole_sequence(dtype, geom):
     m = U.mixer(**geom)
     width = 56
     layer, Pw = _attn_setup(m, width, dtype, seed=geom["heads"])
-    n = [150, 71]
+    n = [400, 71]
     g = torch.Generator().manual_seed(3)
     hs = [torch.randn(k, width, generator=g).bfloat16() for k in n]
     Pd = {k: v.double() for k, v in Pw.items()}
@@ -207,14 +208,14 @@ def test_latent_attention_portions_against_whole_sequence(dtype, geom):
                             m["rot"]["dims"], 1e-5, pos)
         want.append(P.latent_attention(h.double(), c, kr, Pd, m, 1e-5, pos))
     page = 16
-    r2t = ReqToTokenPool(3, 256, DEV)
+    r2t = ReqToTokenPool(3, 512, DEV)
     pool = LatentTokenToKVPool(512, page, dtype, {0: m["kv_rank"] + m["rot_dim"]}, {}, DEV)
     pool.kv_buffer[0].fill_(float("nan"))          # a read of a row that was never written shows
     alloc = PagedTokenToKVPoolAllocator(512, page, dtype, DEV)
     reqs = [Req(rid=str(i), input_ids=[]) for i in range(2)]
     for r in reqs:
         r.req_pool_idx = r2t.alloc(1)[0]
-    cuts = [[40, 2, 23, 31, 1, 1, 1, 51], [3, 64, 1, 1, 1, 1]]
+    cuts = [[290, 2, 23, 31, 1, 1, 1, 51], [3, 64, 1, 1, 1, 1]]   # single tokens past 300 keys: split-KV
     got = [[], []]
     at = [0, 0]
     for step in range(max(len(c) for c in cuts)):
