@@ -114,7 +114,6 @@ fp8_gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   // per-token activation scales, staged once by the epilogue warps: read inside the store loop
   // they cost one serialised L2 round trip PER TOKEN (a load may not be hoisted above the previous
   // token's output store) — 0.1-0.2 us per token, the whole M dependence of this kernel
-  // (profiles/r02_ncu_fp8_smallm_m64_source.md)
   __shared__ float sa_s[MT];
 
   const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);

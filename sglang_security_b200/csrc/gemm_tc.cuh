@@ -182,7 +182,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   // scales, outputs) is touched only after griddep_wait().  The B operand is a WEIGHT in every use of
   // this kernel, so the producer thread puts the first ring stages of its first tile's B in flight
   // before it waits: the TMA fill then overlaps the previous kernel's tail (the mid-M launches are
-  // a chain of fixed latencies, profiles/r02_ncu_fp8_smallm_m64_source.md).
+  // a chain of fixed latencies).
   int b_prefetched = 0;
   if (warp == 0 && lane == 0) {
     if (!MC && item0 < num_items) {
