@@ -227,6 +227,17 @@ int b200_attn_extend_scaled(const void* q, int64_t q_stride, const void* k_cache
                             const int32_t* extend_start_loc, int bs, int max_extend_len, int Hq,
                             int Hkv, int D, int Dv, float scale, float logit_cap, float out_scale,
                             int causal, int dtype, void* stream);
+/* Same kernel with a causal sliding window: the new token at position i attends to the keys
+ * i - window < t <= i (window == 0: all keys up to i).  Key tiles wholly before a CTA's first
+ * visible key are skipped, so the cost follows the window, not the sequence.                    */
+int b200_attn_extend_window(const void* q, int64_t q_stride, const void* k_cache,
+                            const void* v_cache, int64_t kv_row_stride, void* o, int64_t o_stride,
+                            const int32_t* req_to_token, int64_t req_to_token_stride,
+                            const int64_t* req_pool_indices, const int64_t* seq_lens,
+                            const int32_t* extend_prefix_lens, const int32_t* extend_seq_lens,
+                            const int32_t* extend_start_loc, int bs, int max_extend_len, int Hq,
+                            int Hkv, int D, int Dv, float scale, float logit_cap, float out_scale,
+                            int causal, int window, int dtype, void* stream);
 /* FP8 (e4m3) pool -> dense 16-bit rows for the extend kernel (prefill is compute-bound; the extra
  * pass costs 3 bytes/element once per layer): for request b and t < seq_lens[b]
  *   k_out[kv_indptr[b] + t, :] = exact(k_cache[slot(b,t), :]),  dense_rtt[b, t] = kv_indptr[b] + t
@@ -550,6 +561,19 @@ int b200_latent_attn(const float* q_lat, int64_t ldql_t, int64_t ldql_h, const v
                      const float* inv_freq, int rot_dims, int T, int H, int R, int rot, int window,
                      int max_keys, float scale, void* out, int64_t ldo_t, int64_t ldo_h, int num_splits,
                      float* ws, int64_t ws_floats, int dtype, void* stream);
+
+/* Operands of the expanded (per-head) form of the latent attention, for prompt portions (16-bit):
+ *   c_out[n, :R] = cache[slots[n], :R], n < N;   q_out[t, h, :D] = [q[t,h,:dim] | rotary(q[t,h,dim:dim+rot]) | 0]
+ * and, after the up-projection GEMM wrote k_out [N, H, D] (row stride ldk):
+ *   k_out[n, h, dim:dim+rot] = cache[slots[n], R:R+rot]  for every head.                          */
+int b200_latent_expand_gather(const void* cache, int64_t ldc, const int64_t* slots, int N, int R,
+                              void* c_out, int64_t ldco, const void* q, int64_t ldq_t, int64_t ldq_h,
+                              int H, int dim, int rot, int rot_dims, const float* inv_freq,
+                              const int* tok_pos, void* q_out, int D, int T, int dtype, void* stream);
+int b200_latent_expand_rotkeys(const void* cache, int64_t ldc, const int64_t* slots, int N, int R,
+                               int rot, void* k_out, int64_t ldk, int H, int D, int dim, int dtype,
+                               void* stream);
+
 /* Router: z = wr h + br (fp32), the `top` largest logits (ties: lowest index), weights = softmax
  * over the chosen logits; gate[t] = sigmoid(wsg . h) when wsg is given.                           */
 int b200_moe_route(const void* h, int64_t ldh, const float* wr, const float* br, int E, int W,

@@ -166,6 +166,15 @@ _SIGNATURES = {
                                  c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_int, c_float, c_void_p, c_int64, c_int64, c_int, c_void_p,
                                  c_int64, c_int, c_void_p]),
+    "b200_latent_expand_gather": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_int64,
+                                          c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int,
+                                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b200_latent_expand_rotkeys": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p,
+                                           c_int64, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_attn_extend_window": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p,
+                                        c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                        c_float, c_float, c_float, c_int, c_int, c_int, c_void_p]),
     "b200_moe_route": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "b200_moe_align": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),

@@ -47,6 +47,7 @@ struct ExtendParams {
   float logit_cap;
   float out_scale;               // output multiplier (v_scale of an FP8 KV pool; 1 otherwise)
   int causal;
+  int window;                    // causal sliding window: row at position i sees i - window < j <= i (0 = all)
 };
 
 constexpr int kExtThreads = 256;
@@ -114,7 +115,11 @@ attn_extend_kernel(const ExtendParams p) {
   const int head_base = kvh * p.group + (blockIdx.y - kvh * p.head_tiles) * p.pack;
   const int kv_len = prefix + ext;
   const int tok_last = min(tok0 + tok_per_tile, ext) - 1;
-  const int n_kv = p.causal ? ceil_div(prefix + tok_last + 1, kKvTile) : ceil_div(kv_len, kKvTile);
+  const int n_kv_all = p.causal ? ceil_div(prefix + tok_last + 1, kKvTile) : ceil_div(kv_len, kKvTile);
+  // sliding window: the tiles before the first key any row of this CTA sees are skipped; loop
+  // index j stands for key tile j + jb
+  const int jb = (p.causal && p.window > 0) ? max(0, prefix + tok0 - p.window + 1) / kKvTile : 0;
+  const int n_kv = n_kv_all - jb;
   const int64_t q_row0 = p.extend_start[b];
 
   // ---- barriers ----------------------------------------------------------------------------
@@ -176,7 +181,7 @@ attn_extend_kernel(const ExtendParams p) {
     auto load_slots = [&](int j) {
 #pragma unroll
       for (int i = 0; i < PASSES; ++i) {
-        const int pos = j * kKvTile + lrow + RPP * i;
+        const int pos = (j + jb) * kKvTile + lrow + RPP * i;
         slots[i] = (lrow + RPP * i < kKvTile && pos < kv_len) ? __ldg(rtt + pos) : 0;  // 0 = dummy row
       }
     };
@@ -262,6 +267,7 @@ attn_extend_kernel(const ExtendParams p) {
     const int tok = tok0 + r / p.pack;
     const bool row_ok = tok < ext;
     const int limit = p.causal ? prefix + min(tok, ext - 1) : kv_len - 1;  // last visible key
+    const int first = (p.causal && p.window > 0) ? limit - p.window + 1 : 0;  // first visible key
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     const uint32_t tmem_s = tmem_base + lane_addr, tmem_o = tmem_base + lane_addr + C::O_COL;
     const bool capped = p.logit_cap > 0.f;
@@ -272,7 +278,7 @@ attn_extend_kernel(const ExtendParams p) {
     auto score = [&](uint32_t raw, int kpos) -> float {
       float s = __uint_as_float(raw) * p.qk_scale;
       if (capped) s = cap_log2 * fast_tanh(s * inv_cap);
-      return kpos <= limit ? s : -INFINITY;
+      return (kpos <= limit && kpos >= first) ? s : -INFINITY;
     };
 
     for (int j = 0; j < n_kv; ++j) {
@@ -288,13 +294,13 @@ attn_extend_kernel(const ExtendParams p) {
       tc::mbar_arrive(bar_s_free);
       float mt = -INFINITY;
       if constexpr (FAST) {
-        const int k0 = j * kKvTile;
-        if (k0 + kKvTile - 1 > limit) {  // the tile crosses this row's last visible key
+        const int k0 = (j + jb) * kKvTile;
+        if (k0 + kKvTile - 1 > limit || k0 < first) {  // the tile crosses an edge of this row's visible keys
 #pragma unroll
           for (int h = 0; h < 2; ++h)
 #pragma unroll
             for (int c = 0; c < 32; ++c)
-              if (k0 + h * 32 + c > limit) v[h][c] = 0xff800000u;  // -inf
+              if (k0 + h * 32 + c > limit || k0 + h * 32 + c < first) v[h][c] = 0xff800000u;  // -inf
         }
         float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
 #pragma unroll
@@ -312,7 +318,7 @@ attn_extend_kernel(const ExtendParams p) {
         for (int h = 0; h < 2; ++h)
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
-            const float sc = score(v[h][c], j * kKvTile + h * 32 + c);
+            const float sc = score(v[h][c], (j + jb) * kKvTile + h * 32 + c);
             v[h][c] = __float_as_uint(sc);
             mt = fmaxf(mt, sc);
           }
@@ -489,7 +495,23 @@ int b200_attn_extend_scaled(const void* q, int64_t q_stride, const void* k_cache
                             const int32_t* extend_start_loc, int bs, int max_extend_len, int Hq,
                             int Hkv, int D, int Dv, float scale, float logit_cap, float out_scale,
                             int causal, int dtype, void* stream) {
+  return b200_attn_extend_window(q, q_stride, k_cache, v_cache, kv_row_stride, o, o_stride,
+                                 req_to_token, req_to_token_stride, req_pool_indices, seq_lens,
+                                 extend_prefix_lens, extend_seq_lens, extend_start_loc, bs,
+                                 max_extend_len, Hq, Hkv, D, Dv, scale, logit_cap, out_scale, causal,
+                                 0, dtype, stream);
+}
+
+int b200_attn_extend_window(const void* q, int64_t q_stride, const void* k_cache,
+                            const void* v_cache, int64_t kv_row_stride, void* o, int64_t o_stride,
+                            const int32_t* req_to_token, int64_t req_to_token_stride,
+                            const int64_t* req_pool_indices, const int64_t* seq_lens,
+                            const int32_t* extend_prefix_lens, const int32_t* extend_seq_lens,
+                            const int32_t* extend_start_loc, int bs, int max_extend_len, int Hq,
+                            int Hkv, int D, int Dv, float scale, float logit_cap, float out_scale,
+                            int causal, int window, int dtype, void* stream) {
   using namespace b200;
+  B200_REQUIRE(window >= 0 && (window == 0 || causal), "b200_attn_extend: a window needs causal");
   if (bs == 0 || max_extend_len == 0) return 0;
   B200_REQUIRE(q && k_cache && v_cache && o && req_to_token && req_pool_indices && seq_lens &&
                    extend_prefix_lens && extend_seq_lens && extend_start_loc,
@@ -530,6 +552,7 @@ int b200_attn_extend_scaled(const void* q, int64_t q_stride, const void* k_cache
   p.out_scale = out_scale;
   p.qk_scale = logit_cap > 0.f ? scale : scale * 1.4426950408889634f;
   p.causal = causal;
+  p.window = window;
   B200_REQUIRE(bs <= 65535 && Hkv * p.head_tiles <= 65535, "b200_attn_extend: grid too large");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == B200_BF16)

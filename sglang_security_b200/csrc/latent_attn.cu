@@ -318,6 +318,62 @@ static int latent_attn_mma_launch(int grid_x, int grid_y, size_t smem, cudaStrea
   return 0;
 }
 
+// ---- expanded (per-head) keys and values for long prompt portions -------------------------------
+// A portion of a prompt whose tokens outnumber the keys it has to expand is cheaper as ordinary
+// multi-head attention over K_h = [W_uk_h c | kr] and V_h = W_uv_h c (head size D) than over the
+// latent itself (head size R + rot): the two kernels below stage its operands around one GEMM.
+//   blocks [0, N):      c_out[n, :R]  = cache[slots[n], :R]             (A operand of the up-projection)
+//   blocks [N, N + T):  q_out[t, h, :] = [q[t, h, :dim] | rotary(q[t, h, dim:dim+rot]) | 0...]   (D wide)
+template <typename T>
+__global__ void __launch_bounds__(256)
+latent_expand_gather_kernel(const T* __restrict__ cache, int64_t ldc, const int64_t* __restrict__ slots,
+                            int N, int R, T* __restrict__ c_out, int64_t ldco, const T* __restrict__ q,
+                            int64_t ldq_t, int64_t ldq_h, int H, int dim, int rot, int rot_dims,
+                            const float* __restrict__ inv_freq, const int* __restrict__ tok_pos,
+                            T* __restrict__ q_out, int D) {
+  const int blk = blockIdx.x;
+  if (blk < N) {
+    const T* src = cache + slots[blk] * ldc;
+    T* dst = c_out + blk * ldco;
+    for (int d = threadIdx.x; d < R; d += blockDim.x) dst[d] = src[d];
+    return;
+  }
+  const int t = blk - N;
+  const float pos = static_cast<float>(tok_pos[t]);
+  const int dq = dim + rot;
+  for (int e = threadIdx.x; e < H * D; e += blockDim.x) {
+    const int h = e / D, d = e - h * D;
+    const T* qh = q + t * ldq_t + h * ldq_h;
+    float v = 0.f;
+    if (d < dim) {
+      v = to_float<T>(qh[d]);
+    } else if (d < dq) {
+      const int r = d - dim;
+      v = to_float<T>(qh[d]);
+      if ((r | 1) < rot_dims) {                        // pair (2i, 2i + 1) inside the rotated dims
+        const float other = to_float<T>(qh[dim + (r ^ 1)]);
+        float sn, cs;
+        sincosf(pos * inv_freq[r >> 1], &sn, &cs);
+        v = (r & 1) ? v * cs + other * sn : v * cs - other * sn;
+      }
+    }
+    q_out[(static_cast<int64_t>(t) * H + h) * D + d] = from_float<T>(v);
+  }
+}
+
+// kv[n, h, dim + i] = cache[slots[n], R + i] for every head: the rotated key part, shared by all heads
+template <typename T>
+__global__ void __launch_bounds__(256)
+latent_expand_rotkeys_kernel(const T* __restrict__ cache, int64_t ldc, const int64_t* __restrict__ slots,
+                             int R, int rot, T* __restrict__ k_out, int64_t ldk, int H, int D, int dim) {
+  const T* src = cache + slots[blockIdx.x] * ldc + R;
+  T* dst = k_out + blockIdx.x * ldk + dim;
+  for (int e = threadIdx.x; e < H * rot; e += blockDim.x) {
+    const int h = e / rot, i = e - h * rot;
+    dst[h * D + i] = src[i];
+  }
+}
+
 static bool latent_attn_mma_enabled() {
   static const bool on = [] {
     const char* e = std::getenv("B200_LATENT_ATTN_MMA");
@@ -413,4 +469,51 @@ extern "C" int b200_latent_attn(const float* q_lat, int64_t ldql_t, int64_t ldql
   if (dtype == B200_F32) GO(float);
 #undef GO
   B200_REQUIRE(false, "b200_latent_attn: dtype %d", dtype);
+}
+
+extern "C" int b200_latent_expand_gather(const void* cache, int64_t ldc, const int64_t* slots, int N,
+                                         int R, void* c_out, int64_t ldco, const void* q,
+                                         int64_t ldq_t, int64_t ldq_h, int H, int dim, int rot,
+                                         int rot_dims, const float* inv_freq, const int* tok_pos,
+                                         void* q_out, int D, int T, int dtype, void* stream) {
+  using namespace b200;
+  if (N + T == 0) return 0;
+  B200_REQUIRE(cache && slots && c_out && q && tok_pos && q_out, "b200_latent_expand_gather: null pointer");
+  B200_REQUIRE(N >= 0 && T >= 0 && R > 0 && H > 0 && dim >= 0 && rot >= 0 && dim + rot <= D &&
+                   rot_dims <= rot && rot_dims % 2 == 0 && (rot_dims == 0 || inv_freq),
+               "b200_latent_expand_gather: bad sizes (dim %d rot %d D %d rot_dims %d)", dim, rot, D, rot_dims);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer("latent_expand", st);
+#define LAUNCH(TT)                                                                                   \
+  launch_kernel(latent_expand_gather_kernel<TT>, dim3(N + T), dim3(256), 0, st, 1, 0,                \
+                static_cast<const TT*>(cache), ldc, slots, N, R, static_cast<TT*>(c_out), ldco,      \
+                static_cast<const TT*>(q), ldq_t, ldq_h, H, dim, rot, rot_dims, inv_freq, tok_pos,   \
+                static_cast<TT*>(q_out), D)
+  if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
+  else if (dtype == B200_F16) LAUNCH(__half);
+  else B200_REQUIRE(false, "b200_latent_expand_gather: dtype %d", dtype);
+#undef LAUNCH
+  B200_CHECK_LAUNCH("latent_expand_gather_kernel");
+  return 0;
+}
+
+extern "C" int b200_latent_expand_rotkeys(const void* cache, int64_t ldc, const int64_t* slots, int N,
+                                          int R, int rot, void* k_out, int64_t ldk, int H, int D,
+                                          int dim, int dtype, void* stream) {
+  using namespace b200;
+  if (N == 0 || rot == 0) return 0;
+  B200_REQUIRE(cache && slots && k_out && H > 0 && dim >= 0 && dim + rot <= D,
+               "b200_latent_expand_rotkeys: bad arguments");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer("latent_expand", st);
+#define LAUNCH(TT)                                                                                   \
+  launch_kernel(latent_expand_rotkeys_kernel<TT>, dim3(N), dim3(256), 0, st, 1, 0,                   \
+                static_cast<const TT*>(cache), ldc, slots, R, rot, static_cast<TT*>(k_out), ldk, H,  \
+                D, dim)
+  if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
+  else if (dtype == B200_F16) LAUNCH(__half);
+  else B200_REQUIRE(false, "b200_latent_expand_rotkeys: dtype %d", dtype);
+#undef LAUNCH
+  B200_CHECK_LAUNCH("latent_expand_rotkeys_kernel");
+  return 0;
 }

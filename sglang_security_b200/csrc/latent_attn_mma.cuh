@@ -121,21 +121,28 @@ latent_attn_mma_kernel(const float* __restrict__ q_lat, int64_t ldql_t, int64_t 
   const int tl0 = blockIdx.z * per_split, tl1 = min(ntiles, tl0 + per_split);
   const int cpk = (R + rot) / 8;                      // 16-byte chunks per key row (R, rot multiples of 8)
   const int cR = R / 8;
-  auto load_tile = [&](int tl, int buf) {
-    T* dst = k_s + buf * kLaKeys * ldS;
-    const int j0 = lo + tl * kLaKeys;
-    for (int c = tid; c < kLaKeys * cpk; c += kLaThreads) {
-      const int key = c / cpk, ch = c - key * cpk;
-      const int j = j0 + key;
-      if (j > hi) continue;
-      const int64_t slot = r2t[rp * ld_r2t + j];
-      const T* src = cache + slot * ldc + ch * 8;
-      T* d = dst + key * ldS + (ch < cR ? ch * 8 : R16 + (ch - cR) * 8);
-      cp_async16(smem_u32(d), src);
+  // 8 threads copy one key row; a thread reads its key's slot id ONE tile ahead of the copy, so the
+  // gather never waits on the request table
+  const int lkey = tid >> 3, lsub = tid & 7;
+  static_assert(kLaThreads == kLaKeys * 8, "8 loader threads per key");
+  auto slot_of = [&](int tl) -> int64_t {
+    const int j = lo + tl * kLaKeys + lkey;
+    return (tl < tl1 && j <= hi) ? static_cast<int64_t>(r2t[rp * ld_r2t + j]) : -1;
+  };
+  auto load_tile = [&](int buf, int64_t slot) {
+    if (slot >= 0) {
+      const T* src = cache + slot * ldc;
+      T* drow = k_s + (buf * kLaKeys + lkey) * ldS;
+      for (int ch = lsub; ch < cpk; ch += 8)
+        cp_async16(smem_u32(drow + (ch < cR ? ch * 8 : R16 + (ch - cR) * 8)), src + ch * 8);
     }
     cp_async_commit();
   };
-  if (tl0 < tl1) load_tile(tl0, 0);
+  int64_t slot_next = slot_of(tl0);
+  if (tl0 < tl1) {
+    load_tile(0, slot_next);
+    slot_next = slot_of(tl0 + 1);
+  }
   // ---- per-warp state ---------------------------------------------------------------------------
   const int rw = (warp & 3) * 16, chalf = warp >> 2;
   const int g = lane >> 2, tq4 = lane & 3;
@@ -156,14 +163,21 @@ latent_attn_mma_kernel(const float* __restrict__ q_lat, int64_t ldql_t, int64_t 
 #pragma unroll
   for (int n = 0; n < CW / 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
   const float sl2 = scale * 1.4426950408889634f;
+  // a warp whose 16 rows are all padding (a decoded token fills HG of the 64 rows) only helps to
+  // load the key tiles: it issues no ldmatrix / mma and writes nothing
+  const bool warp_has_rows = rw < (ntok - 1) * HG + nh;
   const uint32_t q_base = smem_u32(q_s + (rw + (lane & 15)) * ldS + (lane >> 4) * 8);
   const int col0 = chalf * CW;
 
   for (int tl = tl0; tl < tl1; ++tl) {
     cp_async_wait<0>();
     __syncthreads();
-    if (tl + 1 < tl1) load_tile(tl + 1, (tl + 1 - tl0) & 1);
+    if (tl + 1 < tl1) {
+      load_tile((tl + 1 - tl0) & 1, slot_next);
+      slot_next = slot_of(tl + 2);
+    }
     const T* kt = k_s + ((tl - tl0) & 1) * kLaKeys * ldS;
+    if (!warp_has_rows) continue;
     // S = Q K^T : 16 rows x 32 keys
     float s[4][4];
 #pragma unroll

@@ -10,8 +10,17 @@ coordinates, value size `vdim`, latent size R):
     q_lat[h] = W_uk[h]^T q[h, :dim]                   (absorbed key up-projection, fp32 result)
     p  = softmax_j((q_lat[h] . c_j + rotary(q[h, dim:]) . kr_j) * scale)   over the visible keys
     out = W_o concat_h(W_uv[h] sum_j p_j c_j)
-Only c and kr are cached, and the same kernel runs prompt portions and decoded tokens, so a
-position's result does not depend on how the sequence was cut into steps."""
+Only c and kr are cached.  Two forms of the same sum run on them:
+  * absorbed (above): every query attends to the latent rows themselves, head size R + rot_dim.
+    It needs nothing per key but the cached row, so it serves decoded tokens and short portions
+    (and every step of a 32-bit engine).
+  * expanded: for a step whose new tokens outweigh the keys they see, K_j[h] = [W_uk[h] c_j | kr_j]
+    and V_j[h] = W_uv[h] c_j are formed once per visible key by one GEMM and the step runs as
+    ordinary causal windowed multi-head attention of head size max(dim + rot_dim, vdim) (padded to
+    64 or 128) on the tcgen05 extend kernel: (dim + rot_dim + vdim) instead of (2 R + rot_dim)
+    multiply-adds per score.  16-bit engines only; chosen per step by a cost estimate.
+Both read the cache only, so a position's result does not depend on how the sequence was cut into
+steps or batched, beyond rounding."""
 from __future__ import annotations
 
 from typing import Optional
@@ -25,6 +34,19 @@ from ..rotary_embedding import InterleavedRotary
 
 
 _SM_COUNT = 148      # B200
+# relative speed of the kernels in the cost estimate that picks the form of a step: the library GEMM
+# and the tcgen05 extend kernel against the mma.sync latent kernel, and the most scratch the expanded
+# keys and values may take
+_GEMM_SPEEDUP, _EXTEND_SPEEDUP, _EXPAND_MAX_BYTES = 10.0, 4.0, 1 << 30
+
+
+def _visible_pairs(prefix: int, new: int, window: int) -> int:
+    """Number of (query, key) pairs of `new` tokens after `prefix` cached ones under a causal window."""
+    a = prefix + 1
+    if not window:
+        return new * a + new * (new - 1) // 2
+    k = min(max(window - a, 0), new)
+    return k * a + k * (k - 1) // 2 + (new - k) * window
 
 
 def _bmm_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
@@ -38,6 +60,10 @@ def _bmm_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 
 class LatentAttention(nn.Module):
+    # None: the cost estimate picks the form of every step; "absorbed" / "expanded" pin it (A/B
+    # measurements and tests; "expanded" still falls back where that form does not exist)
+    force_form: Optional[str] = None
+
     def __init__(self, width: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int,
                  q_rank: int, scale: float, layer_id: int, eps: float, window: Optional[int] = None,
                  rope_base: float = 10000.0, rope_dims: Optional[int] = None,
@@ -61,6 +87,9 @@ class LatentAttention(nn.Module):
         self.rotary = InterleavedRotary(rot_dim if rope_dims is None else rope_dims, rope_base)
         if self.rotary.dims > rot_dim:
             raise ValueError("rotary dims exceed the rotated part of a head")
+        need = max(dim + rot_dim, vdim)
+        self.expand_dim = 64 if need <= 64 else (128 if need <= 128 else 0)   # 0: no expanded form
+        self._w_expand = None
 
     # ---- checkpoint tensors ([out, in]) -> the layouts above ------------------------------------
     def load_down(self, w_dq: torch.Tensor, w_dkv: Optional[torch.Tensor]) -> None:
@@ -69,9 +98,97 @@ class LatentAttention(nn.Module):
 
     def load_uk(self, w: torch.Tensor) -> None:      # [H * dim, R]
         self.w_uk.data.copy_(w.view(self.heads, self.dim, self.kv_rank))
+        self._w_expand = None
 
     def load_uv(self, w: torch.Tensor) -> None:      # [H * vdim, R] -> [H, R, vdim]
         self.w_uv_t.data.copy_(w.view(self.heads, self.vdim, self.kv_rank).transpose(1, 2))
+        self._w_expand = None
+
+    # ---- expanded form ---------------------------------------------------------------------------
+    def _expand_weight(self) -> torch.Tensor:
+        """[2 * H * D, R]: rows (h, d < dim) = W_uk[h], rows H*D + (h, d < vdim) = W_uv[h], zero
+        elsewhere, so one GEMM writes keys and values in the head-major layout the kernel reads."""
+        if self._w_expand is None:
+            H, D = self.heads, self.expand_dim
+            w = torch.zeros((2, H, D, self.kv_rank), dtype=self.w_uk.dtype, device=self.w_uk.device)
+            w[0, :, :self.dim] = self.w_uk
+            w[1, :, :self.vdim] = self.w_uv_t.transpose(1, 2)
+            self._w_expand = w.view(2 * H * D, self.kv_rank)
+        return self._w_expand
+
+    def _expand_plan(self, fb):
+        """The step's gather tables for the expanded form, or False when the absorbed form is the
+        cheaper one.  Shared by the layers of equal window through fb.extra."""
+        key = ("latent_expand", self.window, self.heads, self.kv_rank, self.rot_dim, self.expand_dim)
+        if key in fb.extra:
+            return fb.extra[key]
+        plan = fb.extra[key] = self._make_expand_plan(fb)
+        return plan
+
+    def _make_expand_plan(self, fb):
+        pre, ext = fb.extend_prefix_lens_cpu, fb.extend_seq_lens_cpu
+        forced = self.force_form
+        if not self.expand_dim or pre is None or ext is None or forced == "absorbed":
+            return False
+        if forced != "expanded" and max(ext) < 16:
+            return False
+        H, D, R, W = self.heads, self.expand_dim, self.kv_rank, self.window
+        lo = [max(0, p - W + 1) if W else 0 for p in pre]
+        n = [p + e - l for p, e, l in zip(pre, ext, lo)]
+        N = sum(n)
+        if N * 2 * H * D * 2 > _EXPAND_MAX_BYTES and forced != "expanded":
+            return False
+        pairs = sum(_visible_pairs(p, e, W) for p, e in zip(pre, ext))
+        tiles = sum(((e + 127) // 128 * 128) * ((min(k, (W or k) + 128) + 63) // 64 * 64)
+                    for e, k in zip(ext, n))                    # what the 128 x 64 tiled kernel touches
+        absorbed = pairs * H * (2 * R + self.rot_dim)
+        expanded = N * 2 * H * D * R / _GEMM_SPEEDUP + tiles * H * 2 * D / _EXTEND_SPEEDUP
+        if forced != "expanded" and expanded >= absorbed:
+            return False
+        dev = fb.req_pool_indices.device
+        bs = len(ext)
+        off = [0] * bs
+        for b in range(1, bs):
+            off[b] = off[b - 1] + n[b - 1]
+        key_b = torch.repeat_interleave(torch.arange(bs), torch.tensor(n))
+        key_pos = torch.cat([torch.arange(l, l + k) for l, k in zip(lo, n)])
+        host = torch.tensor([off, [p - l for p, l in zip(pre, lo)], n], dtype=torch.int64)
+        tab = host.to(dev, non_blocking=True)
+        kb, kp = key_b.to(dev, non_blocking=True), key_pos.to(dev, non_blocking=True)
+        r2t = fb.req_to_token_pool.req_to_token
+        slots = r2t[fb.req_pool_indices[kb], kp].to(torch.int64)
+        max_n = max(n)
+        rtt = (tab[0][:, None] + torch.arange(max_n, device=dev)[None, :]).to(torch.int32).contiguous()
+        return dict(N=N, slots=slots, rtt=rtt, prefix=tab[1].to(torch.int32), seq=tab[2].contiguous(),
+                    rows=torch.arange(bs, dtype=torch.int64, device=dev), max_ext=max(ext))
+
+    def _forward_expanded(self, q3: torch.Tensor, cache: torch.Tensor, plan, fb) -> torch.Tensor:
+        lib = _lib.load()
+        t, H, D, R, N = q3.shape[0], self.heads, self.expand_dim, self.kv_rank, plan["N"]
+        code = _lib.dtype_code(q3.dtype)
+        c_g = torch.empty((N, R), dtype=q3.dtype, device=q3.device)
+        q_x = torch.empty((t, H, D), dtype=q3.dtype, device=q3.device)
+        rc = lib.b200_latent_expand_gather(
+            cache.data_ptr(), cache.stride(0), plan["slots"].data_ptr(), N, R, c_g.data_ptr(), c_g.stride(0),
+            q3.data_ptr(), q3.stride(0), q3.stride(1), H, self.dim, self.rot_dim, self.rotary.dims,
+            _lib.ptr(self.rotary.inv_freq), fb.tok_pos.data_ptr(), q_x.data_ptr(), D, t, code,
+            _lib.current_stream())
+        _lib.check(rc, "b200_latent_expand_gather")
+        kv = torch.matmul(c_g, self._expand_weight().t())                          # [N, 2 * H * D]
+        rc = lib.b200_latent_expand_rotkeys(
+            cache.data_ptr(), cache.stride(0), plan["slots"].data_ptr(), N, R, self.rot_dim,
+            kv.data_ptr(), kv.stride(0), H, D, self.dim, code, _lib.current_stream())
+        _lib.check(rc, "b200_latent_expand_rotkeys")
+        o_x = torch.empty((t, H, D), dtype=q3.dtype, device=q3.device)
+        esz = kv.element_size()
+        rc = lib.b200_attn_extend_window(
+            q_x.data_ptr(), H * D, kv.data_ptr(), kv.data_ptr() + H * D * esz, kv.stride(0),
+            o_x.data_ptr(), H * D, plan["rtt"].data_ptr(), plan["rtt"].stride(0), plan["rows"].data_ptr(),
+            plan["seq"].data_ptr(), plan["prefix"].data_ptr(), fb.ext_len.data_ptr(),
+            fb.ext_start.data_ptr(), fb.batch_size, plan["max_ext"], H, H, D, D, self.scale, 0.0, 1.0, 1,
+            self.window, code, _lib.current_stream())
+        _lib.check(rc, "b200_attn_extend_window")
+        return o_x[:, :, :self.vdim].reshape(t, H * self.vdim)
 
     def forward(self, h: torch.Tensor, forward_batch) -> torch.Tensor:
         fb = forward_batch
@@ -93,6 +210,10 @@ class LatentAttention(nn.Module):
         _lib.check(rc, "b200_latent_prep")
         q, _ = self.q_up_proj(cq)
         q3 = q.view(t, self.heads, self.dim + self.rot_dim)
+        plan = self._expand_plan(fb) if h.dtype != torch.float32 else False
+        if plan:
+            out, _ = self.o_proj(self._forward_expanded(q3, cache, plan, fb))
+            return out
         q_lat = _bmm_f32(q3[:, :, :self.dim].transpose(0, 1), self.w_uk)           # [H, T, R] fp32
         o_lat = torch.empty((self.heads, t, self.kv_rank), dtype=h.dtype, device=h.device)
         # few tokens with many keys each (decoding): spread every token's keys over several CTAs

@@ -112,9 +112,17 @@ def bench_desirax(name, s, steps, warmup, device="cuda"):
     ms = _timed(prefill, steps, warmup)
     ntok = W["prefill_reqs"] * W["prefill_len"]
     row["prefill_ms"], row["prefill_tokens_per_s"] = round(ms, 3), round(ntok / ms * 1e3)
-    attn_names = ["latent_attn", "latent_prep", "moe_grouped_gemm", "moe_route", "moe_align",
-                  "scalar_rmsnorm_shift", "residual_combine", "act_and_mul"]
+    attn_names = ["latent_attn", "attn_extend", "latent_expand", "latent_prep", "moe_grouped_gemm",
+                  "moe_route", "moe_align", "scalar_rmsnorm_shift", "residual_combine", "act_and_mul"]
     row["prefill_kernels"] = _kernel_times(prefill, attn_names)
+    # the same prompts with the attention pinned to its absorbed (latent) form
+    from ..layers.attention.latent_attention import LatentAttention
+    LatentAttention.force_form = "absorbed"
+    try:
+        row["prefill_absorbed_ms"] = round(_timed(prefill, steps, warmup), 3)
+        row["prefill_absorbed_kernels"] = _kernel_times(prefill, ["latent_attn"])
+    finally:
+        LatentAttention.force_form = None
     # decode: bs requests at the decode context
     reqs = [Req(rid=f"d{i}", input_ids=rnd(W["decode_ctx"])) for i in range(W["decode_bs"])]
     for r in reqs:
@@ -135,6 +143,8 @@ def bench_desirax(name, s, steps, warmup, device="cuda"):
     # latent attention, algorithmic work of one launch (all tokens, one layer)
     keys_prefill = sum(min(p + 1, s["window"]) for p in range(W["prefill_len"])) * W["prefill_reqs"]
     row["latent_attn_prefill_flops"] = 2 * keys_prefill * H * (2 * R + rot)
+    d_exp = 64 if max(s["dim"] + rot, s["vdim"]) <= 64 else 128
+    row["expanded_attn_prefill_flops"] = 2 * keys_prefill * H * 2 * d_exp
     keys_decode = W["decode_bs"] * min(W["decode_ctx"] + 1, s["window"])
     row["latent_attn_decode_bytes"] = keys_decode * (R + rot) * 2
     row["latent_attn_decode_flops"] = 2 * keys_decode * H * (2 * R + rot)

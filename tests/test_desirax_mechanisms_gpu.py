@@ -175,19 +175,24 @@ def _attn_setup(m, width, dtype, seed):
     return layer, Pw
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype,form", [(torch.float32, None), (torch.bfloat16, None),
+                                        (torch.bfloat16, "absorbed"), (torch.bfloat16, "expanded")])
 @pytest.mark.parametrize("geom", [
     dict(heads=3, dim=24, rot_dim=8, vdim=20, kv_rank=40, q_rank=24, window=9),
     dict(heads=8, dim=16, rot_dim=16, vdim=32, kv_rank=64, q_rank=48, window=33, rot_dims=8),
     dict(heads=1, dim=8, rot_dim=4, vdim=8, kv_rank=24, q_rank=8, window=1),
     dict(heads=10, dim=32, rot_dim=32, vdim=48, kv_rank=160, q_rank=64, window=None),
     dict(heads=5, dim=64, rot_dim=64, vdim=64, kv_rank=288, q_rank=96, window=70),
+    dict(heads=2, dim=48, rot_dim=16, vdim=128, kv_rank=72, q_rank=40, window=130),
+    dict(heads=2, dim=96, rot_dim=64, vdim=40, kv_rank=64, q_rank=40, window=65),     # no expanded form
 ])
-def test_latent_attention_portions_against_whole_sequence(dtype, geom):
+def test_latent_attention_portions_against_whole_sequence(dtype, form, geom):
     """Portions of unequal size (two requests side by side, one also decoded token by token) against
     the plain attention over the whole sequence: window edges, 32-key tile edges and page edges are
     all crossed; the single tokens of the long request see more than 128 keys where there is no
-    window, which is where the 16-bit path spreads a token's keys over several CTAs."""
+    window, which is where the 16-bit path spreads a token's keys over several CTAs.  `form` pins
+    the absorbed or the expanded form of the sum for every step (None: the layer's own choice, which
+    takes long portions expanded and single tokens absorbed, so both meet in one sequence)."""
     import desirax_util as U
     from sglang_security_b200.managers.schedule_batch import Req, StepItem, prepare
     from sglang_security_b200.mem_cache.latent_pool import LatentTokenToKVPool, SeqStatePool
@@ -197,6 +202,7 @@ def test_latent_attention_portions_against_whole_sequence(dtype, geom):
     m = U.mixer(**geom)
     width = 56
     layer, Pw = _attn_setup(m, width, dtype, seed=geom["heads"])
+    layer.force_form = form
     n = [400, 71]
     g = torch.Generator().manual_seed(3)
     hs = [torch.randn(k, width, generator=g).bfloat16() for k in n]
