@@ -199,13 +199,15 @@ moe_grouped_gemm_kernel(const T* __restrict__ a, int64_t lda, const T* __restric
   }
 }
 
-// Tensor-core instance for 16-bit types (K a multiple of 8, 16-byte aligned rows): 64 sorted rows of
+// Tensor-core instance for 16-bit types (K a multiple of 8, 16-byte aligned rows): TM sorted rows of
 // one expert x 64 output columns (gated: 64 gate + the 64 matching up columns) per CTA, K in steps of
-// 64 through a cp.async double buffer, 4 warps x (16 rows x 64 columns) of mma.sync m16n8k16, fp32
+// 64 through a cp.async double buffer, 4 warps x (TM / 4 rows x 64 columns) of mma.sync m16n8k16, fp32
 // accumulation; the gated epilogue applies act(gate) * up on the fp32 accumulators.
-constexpr int kTM = 64, kTN = 64, kTK = 64, kTLd = kTK + 8;
+// TM sorted rows per CTA (64 or 128) on 4 warps of TM / 4 rows x 64 columns: long portions take
+// the larger tile, where every weight fragment read from shared memory feeds two row fragments.
+constexpr int kTN = 64, kTK = 64, kTLd = kTK + 8;
 
-template <typename T, bool GATED>
+template <typename T, bool GATED, int TM>
 __global__ void __launch_bounds__(128)
 moe_grouped_gemm_mma_kernel(const T* __restrict__ a, int64_t lda, const T* __restrict__ w, int64_t ldw,
                             int64_t w_expert_stride, const int* __restrict__ offsets,
@@ -213,27 +215,29 @@ moe_grouped_gemm_mma_kernel(const T* __restrict__ a, int64_t lda, const T* __res
                             T* __restrict__ out, int64_t ldo, int act) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int NB = GATED ? 2 * kTN : kTN;
-  T* As = reinterpret_cast<T*>(smem_raw);            // [2][kTM][kTLd]
-  T* Bs = As + 2 * kTM * kTLd;                       // [2][NB][kTLd]
-  __shared__ int rows[kTM];
+  constexpr int NT = 128;                            // 4 warps
+  constexpr int RW = TM / 64;                        // 16-row fragments per warp
+  T* As = reinterpret_cast<T*>(smem_raw);            // [2][TM][kTLd]
+  T* Bs = As + 2 * TM * kTLd;                       // [2][NB][kTLd]
+  __shared__ int rows[TM];
   int e = 0, tile = blockIdx.x, lo = 0, hi = 0;
   for (; e < E; ++e) {
     lo = offsets[e];
     hi = offsets[e + 1];
-    const int nt = (hi - lo + kTM - 1) / kTM;
+    const int nt = (hi - lo + TM - 1) / TM;
     if (tile < nt) break;
     tile -= nt;
   }
   if (e >= E) return;
-  const int m0 = lo + tile * kTM, mcount = min(kTM, hi - m0);
+  const int m0 = lo + tile * TM, mcount = min(TM, hi - m0);
   const int n0 = blockIdx.y * kTN;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (tid < kTM) rows[tid] = tid < mcount ? sorted_rows[m0 + tid] : -1;
+  if (tid < TM) rows[tid] = tid < mcount ? sorted_rows[m0 + tid] : -1;
   __syncthreads();
   const T* we = w + e * w_expert_stride;
   auto load_tile = [&](int k0, int buf) {
-    T* ad = As + buf * kTM * kTLd;
-    for (int c = tid; c < kTM * (kTK / 8); c += 128) {
+    T* ad = As + buf * TM * kTLd;
+    for (int c = tid; c < TM * (kTK / 8); c += NT) {
       const int r = c >> 3, ch = c & 7;
       T* d = ad + r * kTLd + ch * 8;
       if (r < mcount && k0 + ch * 8 < K) {
@@ -244,7 +248,7 @@ moe_grouped_gemm_mma_kernel(const T* __restrict__ a, int64_t lda, const T* __res
       }
     }
     T* bd = Bs + buf * NB * kTLd;
-    for (int c = tid; c < NB * (kTK / 8); c += 128) {
+    for (int c = tid; c < NB * (kTK / 8); c += NT) {
       const int r = c >> 3, ch = c & 7;
       const int half = r / kTN, n = n0 + (r - half * kTN);
       T* d = bd + r * kTLd + ch * 8;
@@ -255,56 +259,70 @@ moe_grouped_gemm_mma_kernel(const T* __restrict__ a, int64_t lda, const T* __res
     }
     cp_async_commit();
   };
-  float acc[8][4], acc2[GATED ? 8 : 1][4];
+  float acc[RW][8][4], acc2[RW][GATED ? 8 : 1][4];
 #pragma unroll
-  for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+  for (int f = 0; f < RW; ++f) {
 #pragma unroll
-  for (int n = 0; n < (GATED ? 8 : 1); ++n) acc2[n][0] = acc2[n][1] = acc2[n][2] = acc2[n][3] = 0.f;
+    for (int n = 0; n < 8; ++n) acc[f][n][0] = acc[f][n][1] = acc[f][n][2] = acc[f][n][3] = 0.f;
+#pragma unroll
+    for (int n = 0; n < (GATED ? 8 : 1); ++n)
+      acc2[f][n][0] = acc2[f][n][1] = acc2[f][n][2] = acc2[f][n][3] = 0.f;
+  }
   const int nk = (K + kTK - 1) / kTK;
   load_tile(0, 0);
   for (int kt = 0; kt < nk; ++kt) {
     cp_async_wait<0>();
     __syncthreads();
     if (kt + 1 < nk) load_tile((kt + 1) * kTK, (kt + 1) & 1);
-    const T* at = As + (kt & 1) * kTM * kTLd;
+    const T* at = As + (kt & 1) * TM * kTLd;
     const T* bt = Bs + (kt & 1) * NB * kTLd;
-    const uint32_t a_base = smem_u32(at + (warp * 16 + (lane & 15)) * kTLd + (lane >> 4) * 8);
+    const uint32_t a_base = smem_u32(at + (warp * 16 * RW + (lane & 15)) * kTLd + (lane >> 4) * 8);
     const uint32_t b_base = smem_u32(bt + ((lane & 7) + ((lane >> 4) << 3)) * kTLd + ((lane >> 3) & 1) * 8);
 #pragma unroll
     for (int ks = 0; ks < kTK; ks += 16) {
-      uint32_t af[4];
-      ldsm_x4(af[0], af[1], af[2], af[3], a_base + ks * 2);
+      uint32_t af[RW][4];
+#pragma unroll
+      for (int f = 0; f < RW; ++f)
+        ldsm_x4(af[f][0], af[f][1], af[f][2], af[f][3], a_base + (f * 16 * kTLd + ks) * 2);
 #pragma unroll
       for (int np = 0; np < 4; ++np) {
         uint32_t b0, b1, b2, b3;
         ldsm_x4(b0, b1, b2, b3, b_base + (np * 16 * kTLd + ks) * 2);
-        mma16816<T>(acc[2 * np], af, b0, b1);
-        mma16816<T>(acc[2 * np + 1], af, b2, b3);
+#pragma unroll
+        for (int f = 0; f < RW; ++f) {
+          mma16816<T>(acc[f][2 * np], af[f], b0, b1);
+          mma16816<T>(acc[f][2 * np + 1], af[f], b2, b3);
+        }
         if (GATED) {
           ldsm_x4(b0, b1, b2, b3, b_base + ((kTN + np * 16) * kTLd + ks) * 2);
-          mma16816<T>(acc2[GATED ? 2 * np : 0], af, b0, b1);
-          mma16816<T>(acc2[GATED ? 2 * np + 1 : 0], af, b2, b3);
+#pragma unroll
+          for (int f = 0; f < RW; ++f) {
+            mma16816<T>(acc2[f][GATED ? 2 * np : 0], af[f], b0, b1);
+            mma16816<T>(acc2[f][GATED ? 2 * np + 1 : 0], af[f], b2, b3);
+          }
         }
       }
     }
   }
   const int g = lane >> 2, t4 = lane & 3;
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int lr = warp * 16 + g + 8 * i;
-    if (lr >= mcount) continue;
-    const int64_t orow = GATED ? m0 + lr : rows[lr];
+  for (int f = 0; f < RW; ++f)
 #pragma unroll
-    for (int n = 0; n < 8; ++n)
+    for (int i = 0; i < 2; ++i) {
+      const int lr = warp * 16 * RW + f * 16 + g + 8 * i;
+      if (lr >= mcount) continue;
+      const int64_t orow = GATED ? m0 + lr : rows[lr];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int col = n0 + n * 8 + 2 * t4 + c;
-        if (col >= Nout) continue;
-        const float v = GATED ? moe_act(acc[n][2 * i + c], act) * acc2[GATED ? n : 0][2 * i + c]
-                              : acc[n][2 * i + c];
-        out[orow * ldo + col] = from_float<T>(v);
-      }
-  }
+      for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int col = n0 + n * 8 + 2 * t4 + c;
+          if (col >= Nout) continue;
+          const float v = GATED ? moe_act(acc[f][n][2 * i + c], act) * acc2[f][GATED ? n : 0][2 * i + c]
+                                : acc[f][n][2 * i + c];
+          out[orow * ldo + col] = from_float<T>(v);
+        }
+    }
 }
 
 }  // namespace b200
@@ -358,17 +376,24 @@ extern "C" int b200_moe_grouped_gemm(const void* a, int64_t lda, const void* w, 
   ScopedKernelTimer timer("moe_grouped_gemm", st);
   if ((dtype == B200_BF16 || dtype == B200_F16) && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 &&
       w_expert_stride % 8 == 0 && aligned16(a) && aligned16(w)) {
-    const dim3 tgrid(ceil_div(rows, kTM) + min(E, rows), ceil_div(Nout, kTN));
-    const size_t smem = static_cast<size_t>(2 * kTM + 2 * (gated ? 2 : 1) * kTN) * kTLd * 2;
-#define LAUNCH_TC(TT, G)                                                                             \
+    // 128-row tiles once the experts average two of them; every expert can leave one partly filled tile
+    const int tm = rows >= 256 * E ? 128 : 64;
+    const dim3 tgrid(ceil_div(rows, tm) + min(E, rows), ceil_div(Nout, kTN));
+    const size_t smem = static_cast<size_t>(2 * tm + 2 * (gated ? 2 : 1) * kTN) * kTLd * 2;
+#define LAUNCH_TM(TT, G, TMV)                                                                        \
   do {                                                                                               \
-    auto kern = moe_grouped_gemm_mma_kernel<TT, G>;                                                  \
+    auto kern = moe_grouped_gemm_mma_kernel<TT, G, TMV>;                                             \
     if (smem > 48 * 1024)                                                                            \
       B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,           \
                                         static_cast<int>(smem)));                                    \
-    launch_kernel(kern, tgrid, dim3(128), smem, st, 1, 0, static_cast<const TT*>(a), lda,            \
+    launch_kernel(kern, tgrid, dim3(128), smem, st, 1, 0, static_cast<const TT*>(a), lda,        \
                   static_cast<const TT*>(w), ldw, w_expert_stride, offsets, sorted_rows, E, top,     \
                   Nout, K, static_cast<TT*>(out), ldo, act);                                         \
+  } while (0)
+#define LAUNCH_TC(TT, G)                                                                             \
+  do {                                                                                               \
+    if (tm == 128) LAUNCH_TM(TT, G, 128);                                                            \
+    else LAUNCH_TM(TT, G, 64);                                                                       \
   } while (0)
     if (dtype == B200_BF16) {
       if (gated) LAUNCH_TC(__nv_bfloat16, true);
@@ -378,6 +403,7 @@ extern "C" int b200_moe_grouped_gemm(const void* a, int64_t lda, const void* w, 
       else LAUNCH_TC(__half, false);
     }
 #undef LAUNCH_TC
+#undef LAUNCH_TM
     B200_CHECK_LAUNCH("moe_grouped_gemm_mma_kernel");
     note_variant("moe_grouped_gemm_mma gated%d", gated);
     return 0;

@@ -105,7 +105,29 @@ def test_router_top_k_and_softmax_over_the_chosen(experts, top):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n", [1, 3, 150])
+def test_router_long_portion_matches_each_token_alone(dtype):
+    """A long portion gives every token bit for bit what it gets when routed alone, and the plain
+    router's choice."""
+    from sglang_security_b200.layers.moe.fused_moe import TopKRouter
+
+    torch.manual_seed(4)
+    width, n, experts, top = 200, 1029, 12, 3
+    r = TopKRouter(width, experts, top, bias=True, shared_gate=True).to(DEV)
+    r.weight.data.copy_(torch.randn(experts, width))
+    r.bias.data.copy_(torch.randn(experts))
+    r.shared_gate.data.copy_(torch.randn(width) / 4)
+    h = torch.randn(n, width).to(dtype)
+    ids, wts, gate = r(h.to(DEV))
+    wi, ww = P.route(h.double(), r.weight.double().cpu(), r.bias.double().cpu(), top)
+    assert torch.equal(ids.cpu().long(), wi)
+    assert (wts.cpu().double() - ww).abs().max() < 1e-5
+    for t in (0, 7, 8, 1023, 1024, 1028):
+        i1, w1, g1 = r(h[t:t + 1].to(DEV))
+        assert torch.equal(i1[0], ids[t]) and torch.equal(w1[0], wts[t]) and torch.equal(g1[0], gate[t])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n", [1, 3, 150, 700])      # 700: the 16-bit kernel's 128-row tiles
 def test_experts_grouped_product_and_weighted_combine(dtype, n):
     from sglang_security_b200.layers.moe.fused_moe import FusedExperts, TopKRouter
     from sglang_security_b200.layers.scalar_norm import residual_combine
