@@ -176,3 +176,52 @@ def test_plain_oracle_token_shift_rotation_and_window():
     l1, l2 = P.forward(cfg, w, t1), P.forward(cfg, w, t2)
     # token 0 reaches position i through the shift (i = 1) and the window (i <= 3) only
     assert not torch.allclose(l1[3], l2[3]) and torch.allclose(l1[5:], l2[5:])
+
+
+def test_expanded_attention_plan_tables_and_choice():
+    """Host side of the expanded attention form: which steps take it, and the gather tables (first
+    gathered key of every request = its window's lower edge, positions shifted to start there)."""
+    from types import SimpleNamespace
+
+    import torch
+
+    from sglang_security_b200.layers.attention.latent_attention import LatentAttention, _visible_pairs
+
+    # (query, key) pairs under a causal window, against the count done by hand
+    for prefix, new, window in [(0, 5, 3), (10, 4, 0), (1, 4, 4), (7, 1, 2), (0, 1, 1), (3, 9, 100)]:
+        want = sum(min(prefix + i + 1, window) if window else prefix + i + 1 for i in range(new))
+        assert _visible_pairs(prefix, new, window) == want
+    layer = LatentAttention(64, heads=4, dim=24, rot_dim=8, vdim=40, kv_rank=256, q_rank=32, scale=0.2,
+                            layer_id=0, eps=1e-5, window=60, params_dtype=torch.bfloat16)
+    assert layer.expand_dim == 64
+    big = LatentAttention(64, heads=2, dim=96, rot_dim=64, vdim=40, kv_rank=48, q_rank=32, scale=0.2,
+                          layer_id=0, eps=1e-5, window=10, params_dtype=torch.bfloat16)
+    assert big.expand_dim == 0                      # heads wider than 128: no expanded form
+    r2t = torch.arange(3 * 200, dtype=torch.int32).view(3, 200) + 1000
+
+    def batch(pre, ext, rows):
+        return SimpleNamespace(extend_prefix_lens_cpu=pre, extend_seq_lens_cpu=ext, extra={},
+                               req_pool_indices=torch.tensor(rows, dtype=torch.int64),
+                               req_to_token_pool=SimpleNamespace(req_to_token=r2t))
+
+    assert layer._expand_plan(batch([50, 60], [1, 1], [0, 1])) is False          # decoding stays absorbed
+    tiny = LatentAttention(64, heads=4, dim=24, rot_dim=8, vdim=40, kv_rank=48, q_rank=32, scale=0.2,
+                           layer_id=0, eps=1e-5, window=4, params_dtype=torch.bfloat16)
+    assert tiny._expand_plan(batch([0], [100], [0])) is False                    # so does a tiny window
+    assert big._expand_plan(batch([0], [150], [0])) is False
+    fb = batch([0, 90, 4], [100, 64, 3], [2, 0, 1])
+    plan = layer._expand_plan(fb)
+    assert plan and layer._expand_plan(fb) is plan                               # one plan per step
+    lo = [0, 31, 0]                                 # 90 - 60 + 1 = 31: the first key the portion's first token sees
+    n = [100, 90 + 64 - 31, 7]
+    assert plan["N"] == sum(n) and plan["max_ext"] == 100
+    assert plan["prefix"].tolist() == [0, 59, 4] and plan["seq"].tolist() == n
+    want_slots = torch.cat([r2t[row, l:l + k] for row, l, k in zip([2, 0, 1], lo, n)]).long()
+    assert torch.equal(plan["slots"], want_slots)
+    off = [0, n[0], n[0] + n[1]]
+    for b in range(3):
+        assert plan["rtt"][b, :n[b]].tolist() == list(range(off[b], off[b] + n[b]))
+    layer.force_form = "absorbed"
+    assert layer._expand_plan(batch([0], [150], [0])) is False
+    layer.force_form = "expanded"
+    assert layer._expand_plan(batch([50], [1], [0]))
