@@ -23,6 +23,7 @@ Both read the cache only, so a position's result does not depend on how the sequ
 steps or batched, beyond rounding."""
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -38,6 +39,10 @@ _SM_COUNT = 148      # B200
 # and the tcgen05 extend kernel against the mma.sync latent kernel, and the most scratch the expanded
 # keys and values may take
 _GEMM_SPEEDUP, _EXTEND_SPEEDUP, _EXPAND_MAX_BYTES = 10.0, 4.0, 1 << 30
+# what the expanded form's extra launches and tables cost per layer, in multiply-adds of the latent
+# kernel (about 0.15 ms): below this saving a step stays absorbed (measured: a 512-token portion beside
+# 32 decoded tokens is faster absorbed, a 2048-token prompt 2 to 4 times faster expanded)
+_EXPAND_FIXED = 6e9
 
 
 def _visible_pairs(prefix: int, new: int, window: int) -> int:
@@ -60,8 +65,9 @@ def _bmm_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 
 class LatentAttention(nn.Module):
-    # None: the cost estimate picks the form of every step; "absorbed" / "expanded" pin it (A/B
-    # measurements and tests; "expanded" still falls back where that form does not exist)
+    # None: the cost estimate picks the form of every step; "absorbed" / "expanded" pin it, "split"
+    # divides every step by the per-entry estimate alone, without the fixed cost (A/B measurements and
+    # tests at small sizes; where the expanded form does not exist the step stays absorbed)
     force_form: Optional[str] = None
 
     def __init__(self, width: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int,
@@ -125,42 +131,74 @@ class LatentAttention(nn.Module):
         plan = fb.extra[key] = self._make_expand_plan(fb)
         return plan
 
+    def _absorbed_takes_subsets(self, fb) -> bool:
+        """Whether the absorbed kernel that would run walks the batch entry by entry (the tiled 16-bit
+        instance does; the CUDA-core one walks all tokens), i.e. whether a step may be divided."""
+        cache = fb.token_to_kv_pool.get_kv_buffer(self.layer_id) if fb.token_to_kv_pool is not None else None
+        return (cache is not None and cache.dtype in (torch.bfloat16, torch.float16)
+                and self.kv_rank % 8 == 0 and self.rot_dim % 8 == 0 and self.kv_rank <= 512
+                and cache.stride(0) % 8 == 0 and os.environ.get("B200_LATENT_ATTN_MMA", "1")[:1] != "0")
+
     def _make_expand_plan(self, fb):
         pre, ext = fb.extend_prefix_lens_cpu, fb.extend_seq_lens_cpu
         forced = self.force_form
         if not self.expand_dim or pre is None or ext is None or forced == "absorbed":
             return False
-        if forced != "expanded" and max(ext) < 16:
-            return False
         H, D, R, W = self.heads, self.expand_dim, self.kv_rank, self.window
+        bs = len(ext)
         lo = [max(0, p - W + 1) if W else 0 for p in pre]
         n = [p + e - l for p, e, l in zip(pre, ext, lo)]
-        N = sum(n)
+        # cost of every entry in either form (multiply-adds weighted by the speed of their kernel)
+        absorbed = [_visible_pairs(p, e, W) * H * (2 * R + self.rot_dim) for p, e in zip(pre, ext)]
+        expanded = [k * 2 * H * D * R / _GEMM_SPEEDUP
+                    + ((e + 127) // 128 * 128) * ((min(k, (W or k) + 128) + 63) // 64 * 64) * H * 2 * D
+                    / _EXTEND_SPEEDUP for e, k in zip(ext, n)]          # 128 x 64 tiles touched
+        if forced == "expanded":
+            take = [True] * bs
+        else:
+            take = [e >= 16 and x < a for e, x, a in zip(ext, expanded, absorbed)]
+            if any(take) and not all(take) and not self._absorbed_takes_subsets(fb):
+                take = [sum(expanded) < sum(absorbed)] * bs              # undivided step: one form for all
+            saved = sum(a - x for a, x, t in zip(absorbed, expanded, take) if t)
+            if forced != "split" and saved < _EXPAND_FIXED:
+                return False
+        B = [b for b in range(bs) if take[b]]
+        if not B:
+            return False
+        N = sum(n[b] for b in B)
         if N * 2 * H * D * 2 > _EXPAND_MAX_BYTES and forced != "expanded":
             return False
-        pairs = sum(_visible_pairs(p, e, W) for p, e in zip(pre, ext))
-        tiles = sum(((e + 127) // 128 * 128) * ((min(k, (W or k) + 128) + 63) // 64 * 64)
-                    for e, k in zip(ext, n))                    # what the 128 x 64 tiled kernel touches
-        absorbed = pairs * H * (2 * R + self.rot_dim)
-        expanded = N * 2 * H * D * R / _GEMM_SPEEDUP + tiles * H * 2 * D / _EXTEND_SPEEDUP
-        if forced != "expanded" and expanded >= absorbed:
-            return False
         dev = fb.req_pool_indices.device
-        bs = len(ext)
-        off = [0] * bs
-        for b in range(1, bs):
-            off[b] = off[b - 1] + n[b - 1]
-        key_b = torch.repeat_interleave(torch.arange(bs), torch.tensor(n))
-        key_pos = torch.cat([torch.arange(l, l + k) for l, k in zip(lo, n)])
-        host = torch.tensor([off, [p - l for p, l in zip(pre, lo)], n], dtype=torch.int64)
+        off, at = [], 0
+        for b in B:
+            off.append(at)
+            at += n[b]
+        key_b = torch.repeat_interleave(torch.tensor(B), torch.tensor([n[b] for b in B]))
+        key_pos = torch.cat([torch.arange(lo[b], lo[b] + n[b]) for b in B])
+        host = torch.tensor([off, [pre[b] - lo[b] for b in B], [n[b] for b in B], B], dtype=torch.int64)
         tab = host.to(dev, non_blocking=True)
         kb, kp = key_b.to(dev, non_blocking=True), key_pos.to(dev, non_blocking=True)
         r2t = fb.req_to_token_pool.req_to_token
         slots = r2t[fb.req_pool_indices[kb], kp].to(torch.int64)
-        max_n = max(n)
+        max_n = max(n[b] for b in B)
         rtt = (tab[0][:, None] + torch.arange(max_n, device=dev)[None, :]).to(torch.int32).contiguous()
-        return dict(N=N, slots=slots, rtt=rtt, prefix=tab[1].to(torch.int32), seq=tab[2].contiguous(),
-                    rows=torch.arange(bs, dtype=torch.int64, device=dev), max_ext=max(ext))
+        plan = dict(N=N, slots=slots, rtt=rtt, prefix=tab[1].to(torch.int32), seq=tab[2].contiguous(),
+                    rows=torch.arange(len(B), dtype=torch.int64, device=dev), bs=len(B),
+                    max_ext=max(ext[b] for b in B), rest=None)
+        if len(B) == bs:
+            plan["ext_len"], plan["ext_start"] = fb.ext_len, fb.ext_start
+            return plan
+        # a divided step: the entries in B run expanded, the others absorbed, each on its own rows
+        A = [b for b in range(bs) if not take[b]]
+        idx_a = torch.tensor(A, dtype=torch.int64).to(dev, non_blocking=True)
+        plan["ext_len"], plan["ext_start"] = fb.ext_len[tab[3]].contiguous(), fb.ext_start[tab[3]].contiguous()
+        in_b = torch.zeros(bs, dtype=torch.bool, device=dev)
+        in_b[tab[3]] = True
+        plan["tok_mask"] = in_b[fb.tok_b.long()]
+        plan["rest"] = dict(bs=len(A), tokens=sum(ext[b] for b in A), max_seq=max(pre[b] + ext[b] for b in A),
+                            ext_len=fb.ext_len[idx_a].contiguous(), ext_start=fb.ext_start[idx_a].contiguous(),
+                            req_pool=fb.req_pool_indices[idx_a].contiguous())
+        return plan
 
     def _forward_expanded(self, q3: torch.Tensor, cache: torch.Tensor, plan, fb) -> torch.Tensor:
         lib = _lib.load()
@@ -179,13 +217,13 @@ class LatentAttention(nn.Module):
             cache.data_ptr(), cache.stride(0), plan["slots"].data_ptr(), N, R, self.rot_dim,
             kv.data_ptr(), kv.stride(0), H, D, self.dim, code, _lib.current_stream())
         _lib.check(rc, "b200_latent_expand_rotkeys")
-        o_x = torch.empty((t, H, D), dtype=q3.dtype, device=q3.device)
+        o_x = (torch.empty if plan["rest"] is None else torch.zeros)((t, H, D), dtype=q3.dtype, device=q3.device)
         esz = kv.element_size()
         rc = lib.b200_attn_extend_window(
             q_x.data_ptr(), H * D, kv.data_ptr(), kv.data_ptr() + H * D * esz, kv.stride(0),
             o_x.data_ptr(), H * D, plan["rtt"].data_ptr(), plan["rtt"].stride(0), plan["rows"].data_ptr(),
-            plan["seq"].data_ptr(), plan["prefix"].data_ptr(), fb.ext_len.data_ptr(),
-            fb.ext_start.data_ptr(), fb.batch_size, plan["max_ext"], H, H, D, D, self.scale, 0.0, 1.0, 1,
+            plan["seq"].data_ptr(), plan["prefix"].data_ptr(), plan["ext_len"].data_ptr(),
+            plan["ext_start"].data_ptr(), plan["bs"], plan["max_ext"], H, H, D, D, self.scale, 0.0, 1.0, 1,
             self.window, code, _lib.current_stream())
         _lib.check(rc, "b200_attn_extend_window")
         return o_x[:, :, :self.vdim].reshape(t, H * self.vdim)
@@ -211,29 +249,46 @@ class LatentAttention(nn.Module):
         q, _ = self.q_up_proj(cq)
         q3 = q.view(t, self.heads, self.dim + self.rot_dim)
         plan = self._expand_plan(fb) if h.dtype != torch.float32 else False
-        if plan:
-            out, _ = self.o_proj(self._forward_expanded(q3, cache, plan, fb))
-            return out
+        if plan and plan["rest"] is None:
+            heads_out = self._forward_expanded(q3, cache, plan, fb)
+        else:
+            heads_out = self._forward_absorbed(q, q3, cache, fb, plan["rest"] if plan else None)
+            if plan:                  # a divided step: long portions expanded, the rest absorbed
+                heads_out = torch.where(plan["tok_mask"][:, None], self._forward_expanded(q3, cache, plan, fb),
+                                        heads_out)
+        out, _ = self.o_proj(heads_out)
+        return out
+
+    def _forward_absorbed(self, q: torch.Tensor, q3: torch.Tensor, cache: torch.Tensor, fb, rest) -> torch.Tensor:
+        """-> [T, H * vdim].  `rest`: the batch entries to run (None: all); rows of other entries are
+        left for the caller to fill."""
+        lib = _lib.load()
+        h, t, inv_freq = q, q.shape[0], self.rotary.inv_freq
+        code = _lib.dtype_code(q.dtype)
         q_lat = _bmm_f32(q3[:, :, :self.dim].transpose(0, 1), self.w_uk)           # [H, T, R] fp32
-        o_lat = torch.empty((self.heads, t, self.kv_rank), dtype=h.dtype, device=h.device)
+        o_lat = (torch.empty if rest is None else torch.zeros)((self.heads, t, self.kv_rank), dtype=h.dtype,
+                                                               device=h.device)
+        max_seq = int(fb.max_seq_len) if rest is None else rest["max_seq"]
+        ext_start, ext_len = (fb.ext_start, fb.ext_len) if rest is None else (rest["ext_start"], rest["ext_len"])
+        req_pool, bs = (fb.req_pool_indices, fb.batch_size) if rest is None else (rest["req_pool"], rest["bs"])
         # few tokens with many keys each (decoding): spread every token's keys over several CTAs
-        keys = min(self.window, int(fb.max_seq_len)) if self.window else int(fb.max_seq_len)
-        ctas = t * ((self.heads + 63) // 64)
+        keys = min(self.window, max_seq) if self.window else max_seq
+        ctas = (t if rest is None else rest["tokens"]) * ((self.heads + 63) // 64)
         splits = 1
         if h.dtype != torch.float32 and ctas < _SM_COUNT and keys > 128:
             splits = max(1, min((keys + 63) // 64, (2 * _SM_COUNT) // ctas, 64))
-        ws = (torch.empty(splits * t * self.heads * (self.kv_rank + 2), dtype=torch.float32, device=h.device)
-              if splits > 1 else None)
+        ws = ((torch.empty if rest is None else torch.zeros)(
+            splits * t * self.heads * (self.kv_rank + 2), dtype=torch.float32, device=h.device)
+            if splits > 1 else None)
         rc = lib.b200_latent_attn(
             q_lat.data_ptr(), q_lat.stride(1), q_lat.stride(0), q.data_ptr(), q3.stride(0), q3.stride(1),
             self.dim, cache.data_ptr(), cache.stride(0), fb.req_to_token_pool.req_to_token.data_ptr(),
-            fb.req_to_token_pool.req_to_token.stride(0), fb.req_pool_indices.data_ptr(),
-            fb.tok_pos.data_ptr(), fb.tok_b.data_ptr(), fb.ext_start.data_ptr(), fb.ext_len.data_ptr(),
-            fb.batch_size, _lib.ptr(inv_freq), self.rotary.dims, t,
-            self.heads, self.kv_rank, self.rot_dim, self.window, int(fb.max_seq_len), self.scale,
+            fb.req_to_token_pool.req_to_token.stride(0), req_pool.data_ptr(),
+            fb.tok_pos.data_ptr(), fb.tok_b.data_ptr(), ext_start.data_ptr(), ext_len.data_ptr(),
+            bs, _lib.ptr(inv_freq), self.rotary.dims, t,
+            self.heads, self.kv_rank, self.rot_dim, self.window, max_seq, self.scale,
             o_lat.data_ptr(), o_lat.stride(1), o_lat.stride(0), splits, _lib.ptr(ws),
             ws.numel() if ws is not None else 0, code, _lib.current_stream())
         _lib.check(rc, "b200_latent_attn")
         v = torch.bmm(o_lat, self.w_uv_t)                                          # [H, T, vdim]
-        out, _ = self.o_proj(v.transpose(0, 1).reshape(t, self.heads * self.vdim))
-        return out
+        return v.transpose(0, 1).reshape(t, self.heads * self.vdim)

@@ -93,7 +93,7 @@ def bench_desirax(name, s, steps, warmup, device="cuda"):
     W = WORK
     bs = max(W["prefill_reqs"], W["decode_bs"])
     tokens = W["decode_bs"] * (W["decode_ctx"] + 64) + W["prefill_reqs"] * W["prefill_len"]
-    runner = ModelRunner(None, torch.bfloat16, max_total_tokens=tokens, max_running_requests=bs,
+    runner = ModelRunner(None, torch.bfloat16, max_total_tokens=tokens, max_running_requests=bs + 1,
                          context_length=max(W["prefill_len"], W["decode_ctx"] + 64), device=device,
                          model=model.eval(), model_config=SimpleNamespace(architecture="Desirax", hf_config=cfg))
     sched = Scheduler(runner)
@@ -139,6 +139,22 @@ def bench_desirax(name, s, steps, warmup, device="cuda"):
     ms = _timed(decode, steps, warmup)
     row["decode_ms"], row["decode_tokens_per_s"] = round(ms, 3), round(W["decode_bs"] / ms * 1e3)
     row["decode_kernels"] = _kernel_times(decode, attn_names)
+    # a mixed step, as the scheduler forms them: every running request decodes one token beside one
+    # 512-token portion of a new prompt (the long portion runs expanded, the decodes absorbed)
+    def mixed():
+        state["n"] += 1
+        assert state["n"] < 60
+        new = Req(rid=f"m{state['n']}", input_ids=rnd(512))
+        assert runner.admit(new)
+        sched.run_step([StepItem(r, [7], want=[0]) for r in reqs] + [StepItem(new, new.input_ids, want=[511])])
+        runner.release(new)
+
+    row["mixed_ms"] = round(_timed(mixed, min(steps, 8), 3), 3)
+    LatentAttention.force_form = "absorbed"
+    try:
+        row["mixed_absorbed_ms"] = round(_timed(mixed, min(steps, 8), 3), 3)
+    finally:
+        LatentAttention.force_form = None
     H, R, rot, Wn = s["heads"], s["kv_rank"], s["rot"], min(s["window"], W["prefill_len"])
     # latent attention, algorithmic work of one launch (all tokens, one layer)
     keys_prefill = sum(min(p + 1, s["window"]) for p in range(W["prefill_len"])) * W["prefill_reqs"]

@@ -197,30 +197,59 @@ def test_expanded_attention_plan_tables_and_choice():
     big = LatentAttention(64, heads=2, dim=96, rot_dim=64, vdim=40, kv_rank=48, q_rank=32, scale=0.2,
                           layer_id=0, eps=1e-5, window=10, params_dtype=torch.bfloat16)
     assert big.expand_dim == 0                      # heads wider than 128: no expanded form
-    r2t = torch.arange(3 * 200, dtype=torch.int32).view(3, 200) + 1000
+    r2t = torch.arange(3 * 2100, dtype=torch.int32).view(3, 2100) + 1000
 
-    def batch(pre, ext, rows):
+    def batch(pre, ext, rows, row_dim=256 + 8):
+        start = [sum(ext[:b]) for b in range(len(ext))]
+        pool = SimpleNamespace(get_kv_buffer=lambda layer_id: torch.zeros(4, row_dim, dtype=torch.bfloat16))
         return SimpleNamespace(extend_prefix_lens_cpu=pre, extend_seq_lens_cpu=ext, extra={},
                                req_pool_indices=torch.tensor(rows, dtype=torch.int64),
-                               req_to_token_pool=SimpleNamespace(req_to_token=r2t))
+                               req_to_token_pool=SimpleNamespace(req_to_token=r2t), token_to_kv_pool=pool,
+                               ext_len=torch.tensor(ext, dtype=torch.int32),
+                               ext_start=torch.tensor(start, dtype=torch.int32),
+                               tok_b=torch.repeat_interleave(torch.arange(len(ext), dtype=torch.int32),
+                                                             torch.tensor(ext)))
 
     assert layer._expand_plan(batch([50, 60], [1, 1], [0, 1])) is False          # decoding stays absorbed
     tiny = LatentAttention(64, heads=4, dim=24, rot_dim=8, vdim=40, kv_rank=48, q_rank=32, scale=0.2,
                            layer_id=0, eps=1e-5, window=4, params_dtype=torch.bfloat16)
-    assert tiny._expand_plan(batch([0], [100], [0])) is False                    # so does a tiny window
+    assert tiny._expand_plan(batch([0], [100], [0], 56)) is False                # so does a tiny window
     assert big._expand_plan(batch([0], [150], [0])) is False
-    fb = batch([0, 90, 4], [100, 64, 3], [2, 0, 1])
+    # at these sizes the saving is below the fixed cost of the expanded form's extra launches
+    assert layer._expand_plan(batch([0, 90], [100, 64], [2, 0])) is False
+    wide = LatentAttention(64, heads=16, dim=64, rot_dim=64, vdim=128, kv_rank=512, q_rank=32, scale=0.2,
+                           layer_id=0, eps=1e-5, window=4096, params_dtype=torch.bfloat16)
+    assert wide._expand_plan(batch([0], [2048], [0], 576))["rest"] is None       # a long prompt: expanded
+    assert wide._expand_plan(batch([0, 150], [40, 1], [0, 1], 576)) is False     # a short one beside a decode: not
+    # a divided step: two long portions expanded, a decoded token and a 3-token portion absorbed
+    layer.force_form = "split"
+    fb = batch([0, 150, 90, 4], [100, 1, 64, 3], [2, 1, 0, 1])
     plan = layer._expand_plan(fb)
     assert plan and layer._expand_plan(fb) is plan                               # one plan per step
-    lo = [0, 31, 0]                                 # 90 - 60 + 1 = 31: the first key the portion's first token sees
-    n = [100, 90 + 64 - 31, 7]
-    assert plan["N"] == sum(n) and plan["max_ext"] == 100
-    assert plan["prefix"].tolist() == [0, 59, 4] and plan["seq"].tolist() == n
-    want_slots = torch.cat([r2t[row, l:l + k] for row, l, k in zip([2, 0, 1], lo, n)]).long()
+    lo = [0, 31]                                    # 90 - 60 + 1 = 31: the first key the portion's first token sees
+    n = [100, 90 + 64 - 31]
+    assert plan["N"] == sum(n) and plan["max_ext"] == 100 and plan["bs"] == 2
+    assert plan["prefix"].tolist() == [0, 59] and plan["seq"].tolist() == n
+    assert plan["ext_len"].tolist() == [100, 64] and plan["ext_start"].tolist() == [0, 101]
+    want_slots = torch.cat([r2t[row, l:l + k] for row, l, k in zip([2, 0], lo, n)]).long()
     assert torch.equal(plan["slots"], want_slots)
-    off = [0, n[0], n[0] + n[1]]
-    for b in range(3):
+    off = [0, n[0]]
+    for b in range(2):
         assert plan["rtt"][b, :n[b]].tolist() == list(range(off[b], off[b] + n[b]))
+    rest = plan["rest"]
+    assert rest["bs"] == 2 and rest["tokens"] == 4 and rest["max_seq"] == 151
+    assert rest["ext_len"].tolist() == [1, 3] and rest["ext_start"].tolist() == [100, 165]
+    assert rest["req_pool"].tolist() == [1, 1]
+    assert plan["tok_mask"].tolist() == [True] * 100 + [False] + [True] * 64 + [False] * 3
+    # all entries long: nothing is left for the absorbed form
+    whole = layer._expand_plan(batch([0, 90], [100, 64], [2, 0]))
+    assert whole and whole["rest"] is None and whole["bs"] == 2
+    # a latent the tiled absorbed kernel does not take (rank not a multiple of 8): the step is not divided
+    odd = LatentAttention(64, heads=4, dim=24, rot_dim=8, vdim=40, kv_rank=252, q_rank=32, scale=0.2,
+                          layer_id=0, eps=1e-5, window=60, params_dtype=torch.bfloat16)
+    odd.force_form = "split"
+    p2 = odd._expand_plan(batch([0, 150, 90, 4], [100, 1, 64, 3], [2, 1, 0, 1], 260))
+    assert p2 is False or p2["rest"] is None
     layer.force_form = "absorbed"
     assert layer._expand_plan(batch([0], [150], [0])) is False
     layer.force_form = "expanded"

@@ -198,7 +198,8 @@ def _attn_setup(m, width, dtype, seed):
 
 
 @pytest.mark.parametrize("dtype,form", [(torch.float32, None), (torch.bfloat16, None),
-                                        (torch.bfloat16, "absorbed"), (torch.bfloat16, "expanded")])
+                                        (torch.bfloat16, "absorbed"), (torch.bfloat16, "expanded"),
+                                        (torch.bfloat16, "split")])
 @pytest.mark.parametrize("geom", [
     dict(heads=3, dim=24, rot_dim=8, vdim=20, kv_rank=40, q_rank=24, window=9),
     dict(heads=8, dim=16, rot_dim=16, vdim=32, kv_rank=64, q_rank=48, window=33, rot_dims=8),
@@ -213,8 +214,9 @@ def test_latent_attention_portions_against_whole_sequence(dtype, form, geom):
     the plain attention over the whole sequence: window edges, 32-key tile edges and page edges are
     all crossed; the single tokens of the long request see more than 128 keys where there is no
     window, which is where the 16-bit path spreads a token's keys over several CTAs.  `form` pins
-    the absorbed or the expanded form of the sum for every step (None: the layer's own choice, which
-    takes long portions expanded and single tokens absorbed, so both meet in one sequence)."""
+    the absorbed or the expanded form of the sum for every step; "split" takes long portions
+    expanded and short ones absorbed inside one step, so both forms meet in one sequence and one
+    batch (None: the layer's own choice, which at these sizes is the absorbed form)."""
     import desirax_util as U
     from sglang_security_b200.managers.schedule_batch import Req, StepItem, prepare
     from sglang_security_b200.mem_cache.latent_pool import LatentTokenToKVPool, SeqStatePool
