@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""bench.py — headline benchmark of the B200 hot path (contract: task prompt / DESIGN.md §6).
+"""bench.py — headline benchmark of the B200 hot path.
 
 Metric (BASELINE.json): decode tokens/s of Llama-3.1-8B FP8 (W8A8: per-channel e4m3 weights, dynamic
 per-token e4m3 activations) at 1/2/4/8 B200, plus the decode-attention kernel's HBM GB/s vs peak.

@@ -1,4 +1,4 @@
-// Tensor-core instance of the latent attention (16-bit storage types): the same contract as
+// Tensor-core instance of the latent attention (16-bit storage types): the same interface as
 // latent_attn_kernel, tiled like a flash attention over the shared latent rows.
 //   CTA  = TQ consecutive tokens of one request x HG heads (<= 64 rows, row = tq * HG + hh), 8 warps:
 //          warp w owns rows 16 * (w & 3) .. +15 and the output columns of half (w >> 2) (CW each), so
