@@ -27,15 +27,46 @@ moe_route_kernel(const T* __restrict__ h, int64_t ldh, const float* __restrict__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T* row = h + t * ldh;
   const int jobs = E + ((wsg && gate) ? 1 : 0);
+  // every token takes the same path, so its sums do not depend on the batch it arrives in
+  const bool vec8 = W % 8 == 0 && ldh % 8 == 0 && (reinterpret_cast<uintptr_t>(h) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(wr) & 15) == 0 &&
+                    (!wsg || (reinterpret_cast<uintptr_t>(wsg) & 15) == 0);
   for (int e = warp; e < jobs; e += 8) {
     const float* w = e < E ? wr + static_cast<int64_t>(e) * W : wsg;
     float s0 = 0.f, s1 = 0.f;
-    int d = lane;
-    for (; d + 32 < W; d += 64) {
-      s0 = fmaf(w[d], to_float<T>(row[d]), s0);
-      s1 = fmaf(w[d + 32], to_float<T>(row[d + 32]), s1);
+    if (vec8) {
+      // a lane takes 8 consecutive coordinates per pass: one 16-byte load of the activations
+      // (two for fp32) against two of the router row
+      for (int d = lane * 8; d < W; d += 256) {
+        float hv[8];
+        if constexpr (sizeof(T) == 2) {
+          const uint4 u = *reinterpret_cast<const uint4*>(row + d);
+          const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) hv[k] = to_float<T>(e[k]);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) hv[k] = to_float<T>(row[d + k]);
+        }
+        const float4 w0 = *reinterpret_cast<const float4*>(w + d);
+        const float4 w1 = *reinterpret_cast<const float4*>(w + d + 4);
+        s0 = fmaf(w0.x, hv[0], s0);
+        s1 = fmaf(w1.x, hv[4], s1);
+        s0 = fmaf(w0.y, hv[1], s0);
+        s1 = fmaf(w1.y, hv[5], s1);
+        s0 = fmaf(w0.z, hv[2], s0);
+        s1 = fmaf(w1.z, hv[6], s1);
+        s0 = fmaf(w0.w, hv[3], s0);
+        s1 = fmaf(w1.w, hv[7], s1);
+      }
+    } else {
+      int d = lane;
+      for (; d + 32 < W; d += 64) {
+        s0 = fmaf(w[d], to_float<T>(row[d]), s0);
+        s1 = fmaf(w[d + 32], to_float<T>(row[d + 32]), s1);
+      }
+      if (d < W) s0 = fmaf(w[d], to_float<T>(row[d]), s0);
     }
-    if (d < W) s0 = fmaf(w[d], to_float<T>(row[d]), s0);
     float s = s0 + s1;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);

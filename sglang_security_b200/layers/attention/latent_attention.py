@@ -144,6 +144,8 @@ class LatentAttention(nn.Module):
         forced = self.force_form
         if not self.expand_dim or pre is None or ext is None or forced == "absorbed":
             return False
+        if forced is None and max(ext) < 16:
+            return False
         H, D, R, W = self.heads, self.expand_dim, self.kv_rank, self.window
         bs = len(ext)
         lo = [max(0, p - W + 1) if W else 0 for p in pre]
