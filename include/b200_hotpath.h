@@ -589,6 +589,72 @@ int b200_moe_grouped_gemm(const void* a, int64_t lda, const void* w, int64_t ldw
                           int top, int rows, int Nout, int K, void* out, int64_t ldo, int gated,
                           int act, int dtype, void* stream);
 
+/* The same router with a score mode: 0 = weights are the softmax over the chosen logits, 1 = the
+ * sigmoid of each chosen logit, not renormalised.                                                 */
+int b200_moe_route_scored(const void* h, int64_t ldh, const float* wr, const float* br, int E, int W,
+                          int top, const float* wsg, int* ids, float* wts, float* gate, int T,
+                          int score, int dtype, void* stream);
+/* The grouped GEMM with a mode: 0 = plain, 1 = gated (as above), 2 = experts without a gate: A rows
+ * gathered like the gated form, w [E][Nout, K], out[m] = act(row_scale[sorted_rows[m]] * acc) with
+ * row_scale fp32 per (token, choice) row or NULL.  act: 0 silu, 1 gelu (tanh form), 2 relu squared. */
+int b200_moe_grouped_gemm_mode(const void* a, int64_t lda, const void* w, int64_t ldw,
+                               int64_t w_expert_stride, const int* offsets, const int* sorted_rows,
+                               int E, int top, int rows, int Nout, int K, void* out, int64_t ldo,
+                               int mode, int act, const float* row_scale, int dtype, void* stream);
+
+/* Norm on a sublayer's output, then the residual add, in fp32:
+ *   y = sa * a + sb * b + sum_k rows[t * top + k]      (each term optional, model dtype)
+ *   x += mult * y / sqrt(mean(y^2) + eps) * w          (w fp32 [W] or NULL)
+ * out_h (model dtype, optional) receives the new x.                                                */
+int b200_add_normed(float* x, int64_t ldx, const void* a, int64_t lda, float sa, const void* b,
+                    int64_t ldb, float sb, const void* rows, int64_t ld_rows, int top, const float* w,
+                    float eps, float mult, void* out_h, int64_t ldh, int T, int W, int dtype,
+                    void* stream);
+/* out (fp32) = cap * tanh(z / cap); cap <= 0 copies.                                               */
+int b200_softcap_rows(const void* z, int64_t ldz, float* out, int64_t ldo, int T, int V, float cap,
+                      int dtype, void* stream);
+
+/* Matrix-state linear recurrence per (batch entry, head) over the entry's new tokens, state fp32:
+ *   S_t = a_t S_(t-1) + b_t k_t v_t^T ;  o_t = S_t^T (q_scale q_t)   [/ den_t]
+ * decay given (fp32 [H]): a_t = decay[h], b_t = 1.  gates given (fp32 [T, 2H], input then forget
+ * pre-activations): li = cap tanh(zi / cap), lf = logsigmoid(cap tanh(zf / cap)) (cap <= 0: uncapped),
+ * m_t = max(lf + m_(t-1), li) with m_0 = 0, a_t = exp(lf + m_(t-1) - m_t), b_t = exp(li - m_t),
+ * n_t = a_t n_(t-1) + b_t k_t, den_t = max(|n_t . q_t|, exp(-m_t)) + den_eps.  act 1 applies silu to
+ * q, k and v first.  q, k [T, H * D], v [T, H * E] (row strides given), out fp32 [T, H * E].  The
+ * state row state[slot[b]] (b200_linear_recurrence_state_width floats) is read unless the entry's
+ * first token is at position 0 and written at the end.                                             */
+int64_t b200_linear_recurrence_state_width(int H, int D, int E, int gated);
+int b200_linear_recurrence(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
+                           int64_t ldv, const float* gates, int64_t ldg, const float* decay, float cap,
+                           float q_scale, float den_eps, int act, float* state, int64_t ld_state,
+                           const int64_t* slot, const int* tok_pos, const int* ext_start,
+                           const int* ext_len, float* out, int64_t ldo, int batch, int H, int D, int E,
+                           int dtype, void* stream);
+/* out = o / sqrt(mean over each group of `group` coordinates (o^2) + eps) * w * sigmoid(z); w and z
+ * optional; o fp32, z and out in the model dtype.                                                  */
+int b200_gated_group_rmsnorm(const float* o, int64_t ldo, const float* w, const void* z, int64_t ldz,
+                             void* out, int64_t ldout, int T, int N, int group, float eps, int dtype,
+                             void* stream);
+
+/* Attention with a sink, step 1: q (H heads) and k (G heads) of size D are RMS-normed in groups of
+ * q_group / k_group coordinates (0 = no norm) with weights qw / kw, rotated (interleaved pairs, first
+ * rot_dims coordinates, angle = position * (freq_hi + freq_lo)); queries go to q_out (fp32), keys to
+ * pool[loc[t]][k_off ...], values (G heads of size E) to pool[loc[t]][v_off ...].                 */
+int b200_qk_norm_rope_write(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
+                            int64_t ldv, const float* qw, const float* kw, int q_group, int k_group,
+                            float eps, const float* freq_hi, const float* freq_lo, int rot_dims,
+                            const int* tok_pos, const int64_t* loc, void* pool, int64_t ld_pool,
+                            int k_off, int v_off, float* q_out, int64_t ldqo, int T, int H, int G,
+                            int D, int E, int dtype, void* stream);
+/* Step 2: token t at position p of request req_idx[tok_b[t]] sees keys j <= p with p - j < window
+ * (window 0: all) or j < keep_first; weights = exp(score) / (sum exp(score) + exp(sink[h])) (sink
+ * NULL: plain softmax); out [T, H * E] in the pool's dtype.                                        */
+int b200_sink_attn(const float* q, int64_t ldq, const void* pool, int64_t ld_pool, int k_off,
+                   int v_off, const int* req_to_token, int64_t ld_r2t, const int64_t* req_idx,
+                   const int* tok_pos, const int* tok_b, const float* sink, float scale, int window,
+                   int keep_first, void* out, int64_t ldo, int T, int H, int G, int D, int E, int dtype,
+                   void* stream);
+
 #ifdef __cplusplus
 }
 #endif

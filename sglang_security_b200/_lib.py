@@ -181,6 +181,30 @@ _SIGNATURES = {
     "b200_moe_grouped_gemm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p,
                                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int64,
                                       c_int, c_int, c_int, c_void_p]),
+    "b200_moe_route_scored": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                      c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b200_moe_grouped_gemm_mode": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p,
+                                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int64,
+                                           c_int, c_int, c_void_p, c_int, c_void_p]),
+    "b200_add_normed": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_float, c_void_p, c_int64, c_float,
+                                c_void_p, c_int64, c_int, c_void_p, c_float, c_float, c_void_p, c_int64,
+                                c_int, c_int, c_int, c_void_p]),
+    "b200_softcap_rows": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_float, c_int,
+                                  c_void_p]),
+    "b200_linear_recurrence_state_width": (c_int64, [c_int, c_int, c_int, c_int]),
+    "b200_linear_recurrence": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
+                                       c_int64, c_void_p, c_float, c_float, c_float, c_int, c_void_p,
+                                       c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                       c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_gated_group_rmsnorm": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
+                                         c_int, c_int, c_int, c_float, c_int, c_void_p]),
+    "b200_qk_norm_rope_write": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
+                                        c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_int,
+                                        c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
+                                        c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_sink_attn": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_int64,
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p,
+                               c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
 }
 
 

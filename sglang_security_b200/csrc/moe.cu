@@ -1,7 +1,8 @@
 // Mixture-of-experts feed-forward, device side only (no host read of the routing result):
 //   moe_route        : router logits z = W_r h + b in fp32, the `top` largest (ties: lowest index),
-//                      weights = softmax over the chosen logits; optionally the per-token gate
-//                      sigmoid(w_sg . h) of a shared expert.  One warp per token.
+//                      weights = softmax over the chosen logits, or (score mode 1) the sigmoid of each
+//                      chosen logit, not renormalised; optionally the per-token gate
+//                      sigmoid(w_sg . h) of a shared expert.  One CTA per token.
 //   moe_align        : stable counting sort of the (token, choice) rows by expert -> row offsets per
 //                      expert and the sorted row list.
 //   moe_grouped_gemm : for every expert, rows[offsets[e] : offsets[e+1]] x W[e]^T with fp32
@@ -9,6 +10,10 @@
 //                      halves of the fused [gate; up] weight are multiplied in one pass and
 //                      act(gate) * up is stored in sorted order; otherwise A is that intermediate and
 //                      the result is scattered back to row t * top + k for the weighted combine.
+//                      ACT form (experts without a gate): A rows gathered like GATED, one weight,
+//                      act(scale[row] * (W h)) stored in sorted order; the optional fp32 scale per
+//                      (token, choice) row is a router weight that multiplies the expert's input,
+//                      applied to the fp32 accumulator (W (s h) = s (W h)).
 #include "common.cuh"
 #include "latent_attn_mma.cuh"   // ldmatrix / mma.sync wrappers
 
@@ -20,7 +25,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ h, int64_t ldh, const float* __restrict__ wr,
                  const float* __restrict__ br, int E, int W, int top, const float* __restrict__ wsg,
-                 int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ gate, int Tn) {
+                 int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ gate, int Tn,
+                 int score) {
   // one CTA per token: its 8 warps share the experts' dot products (and the gate's), warp 0 ranks
   __shared__ float z_s[32 * kMaxExpertsPerLane];
   const int t = blockIdx.x;
@@ -80,7 +86,7 @@ moe_route_kernel(const T* __restrict__ h, int64_t ldh, const float* __restrict__
   float z[kMaxExpertsPerLane];
 #pragma unroll
   for (int i = 0; i < kMaxExpertsPerLane; ++i) z[i] = (lane + 32 * i < E) ? z_s[lane + 32 * i] : -INFINITY;
-  float zmax = 0.f, sum = 0.f, mine = 0.f;  // lane k keeps the k-th chosen logit
+  float zmax = 0.f, sum = 0.f, mine = 0.f, mine_z = 0.f;  // lane k keeps the k-th chosen logit
   for (int k = 0; k < top; ++k) {
     float bv = -INFINITY;
     int bi = 0x7fffffff;
@@ -107,10 +113,13 @@ moe_route_kernel(const T* __restrict__ h, int64_t ldh, const float* __restrict__
       if (bi == lane + 32 * i) z[i] = -INFINITY;
     const float p = expf(bv - zmax);
     sum += p;
-    if (lane == k) mine = p;
+    if (lane == k) {
+      mine = p;
+      mine_z = bv;
+    }
     if (lane == 0) ids[t * top + k] = bi;
   }
-  if (lane < top) wts[t * top + lane] = mine / sum;
+  if (lane < top) wts[t * top + lane] = score == 1 ? 1.0f / (1.0f + expf(-mine_z)) : mine / sum;
 }
 
 __global__ void __launch_bounds__(1024)
@@ -140,18 +149,26 @@ moe_align_kernel(const int* __restrict__ ids, int N, int E, int* __restrict__ of
 
 __device__ __forceinline__ float moe_act(float z, int kind) {
   if (kind == 0) return z / (1.0f + expf(-z));
+  if (kind == 2) {                                   // squared relu
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+  }
   const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
   return 0.5f * z * (1.0f + tanhf(u));
 }
 
 constexpr int kGM = 32, kGN = 64, kGK = 32;
 
-template <typename T, bool GATED>
+// MODE 0: plain (A sorted, result scattered); 1: gated; 2: one weight + activation (see the top)
+template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 moe_grouped_gemm_kernel(const T* __restrict__ a, int64_t lda, const T* __restrict__ w, int64_t ldw,
                         int64_t w_expert_stride, const int* __restrict__ offsets,
                         const int* __restrict__ sorted_rows, int E, int top, int Nout, int K,
-                        T* __restrict__ out, int64_t ldo, int act) {
+                        T* __restrict__ out, int64_t ldo, int act,
+                        const float* __restrict__ row_scale) {
+  constexpr bool GATED = MODE == 1;
+  constexpr bool GATHER = MODE != 0;
   __shared__ float As[kGM][kGK + 1];
   __shared__ float Bs[(GATED ? 2 : 1) * kGN][kGK + 1];
   __shared__ int rows[kGM];
@@ -185,7 +202,7 @@ moe_grouped_gemm_kernel(const T* __restrict__ a, int64_t lda, const T* __restric
       const int r = idx / kGK, k = idx - r * kGK;
       float v = 0.f;
       if (r < mcount && k0 + k < K) {
-        const int64_t src = GATED ? rows[r] / top : m0 + r;
+        const int64_t src = GATHER ? rows[r] / top : m0 + r;
         v = to_float<T>(a[src * lda + k0 + k]);
       }
       As[r][k] = v;
@@ -219,12 +236,14 @@ moe_grouped_gemm_kernel(const T* __restrict__ a, int64_t lda, const T* __restric
   for (int r = 0; r < 2; ++r) {
     const int lr = ty * 2 + r;
     if (lr >= mcount) continue;
-    const int64_t orow = GATED ? m0 + lr : rows[lr];
+    const int64_t orow = GATHER ? m0 + lr : rows[lr];
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       const int n = n0 + tx + 16 * c;
       if (n >= Nout) continue;
-      const float v = GATED ? moe_act(acc[r][c], act) * acc2[r][c] : acc[r][c];
+      float v = acc[r][c];
+      if (GATED) v = moe_act(v, act) * acc2[r][c];
+      else if (MODE == 2) v = moe_act(row_scale ? v * row_scale[rows[lr]] : v, act);
       out[orow * ldo + n] = from_float<T>(v);
     }
   }
@@ -238,12 +257,15 @@ moe_grouped_gemm_kernel(const T* __restrict__ a, int64_t lda, const T* __restric
 // the larger tile, where every weight fragment read from shared memory feeds two row fragments.
 constexpr int kTN = 64, kTK = 64, kTLd = kTK + 8;
 
-template <typename T, bool GATED, int TM>
+template <typename T, int MODE, int TM>
 __global__ void __launch_bounds__(128)
 moe_grouped_gemm_mma_kernel(const T* __restrict__ a, int64_t lda, const T* __restrict__ w, int64_t ldw,
                             int64_t w_expert_stride, const int* __restrict__ offsets,
                             const int* __restrict__ sorted_rows, int E, int top, int Nout, int K,
-                            T* __restrict__ out, int64_t ldo, int act) {
+                            T* __restrict__ out, int64_t ldo, int act,
+                            const float* __restrict__ row_scale) {
+  constexpr bool GATED = MODE == 1;
+  constexpr bool GATHER = MODE != 0;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int NB = GATED ? 2 * kTN : kTN;
   constexpr int NT = 128;                            // 4 warps
@@ -272,7 +294,7 @@ moe_grouped_gemm_mma_kernel(const T* __restrict__ a, int64_t lda, const T* __res
       const int r = c >> 3, ch = c & 7;
       T* d = ad + r * kTLd + ch * 8;
       if (r < mcount && k0 + ch * 8 < K) {
-        const int64_t src = GATED ? rows[r] / top : m0 + r;
+        const int64_t src = GATHER ? rows[r] / top : m0 + r;
         cp_async16(smem_u32(d), a + src * lda + k0 + ch * 8);
       } else {
         *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
@@ -342,15 +364,16 @@ moe_grouped_gemm_mma_kernel(const T* __restrict__ a, int64_t lda, const T* __res
     for (int i = 0; i < 2; ++i) {
       const int lr = warp * 16 * RW + f * 16 + g + 8 * i;
       if (lr >= mcount) continue;
-      const int64_t orow = GATED ? m0 + lr : rows[lr];
+      const int64_t orow = GATHER ? m0 + lr : rows[lr];
 #pragma unroll
       for (int n = 0; n < 8; ++n)
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           const int col = n0 + n * 8 + 2 * t4 + c;
           if (col >= Nout) continue;
-          const float v = GATED ? moe_act(acc[f][n][2 * i + c], act) * acc2[f][GATED ? n : 0][2 * i + c]
-                                : acc[f][n][2 * i + c];
+          float v = acc[f][n][2 * i + c];
+          if (GATED) v = moe_act(v, act) * acc2[f][GATED ? n : 0][2 * i + c];
+          else if (MODE == 2) v = moe_act(row_scale ? v * row_scale[rows[lr]] : v, act);
           out[orow * ldo + col] = from_float<T>(v);
         }
     }
@@ -358,20 +381,21 @@ moe_grouped_gemm_mma_kernel(const T* __restrict__ a, int64_t lda, const T* __res
 
 }  // namespace b200
 
-extern "C" int b200_moe_route(const void* h, int64_t ldh, const float* wr, const float* br, int E,
-                              int W, int top, const float* wsg, int* ids, float* wts, float* gate,
-                              int T, int dtype, void* stream) {
+extern "C" int b200_moe_route_scored(const void* h, int64_t ldh, const float* wr, const float* br,
+                                     int E, int W, int top, const float* wsg, int* ids, float* wts,
+                                     float* gate, int T, int score, int dtype, void* stream) {
   using namespace b200;
   if (T == 0) return 0;
   B200_REQUIRE(h && wr && ids && wts, "b200_moe_route: null pointer");
   B200_REQUIRE(E > 0 && E <= 32 * kMaxExpertsPerLane && top > 0 && top <= E && top <= 32 && W > 0,
                "b200_moe_route: experts %d (max %d), top %d", E, 32 * kMaxExpertsPerLane, top);
+  B200_REQUIRE(score == 0 || score == 1, "b200_moe_route: score mode %d", score);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   ScopedKernelTimer timer("moe_route", st);
   const dim3 grid(T);
 #define LAUNCH(TT)                                                                                   \
   launch_kernel(moe_route_kernel<TT>, grid, dim3(256), 0, st, 1, 0, static_cast<const TT*>(h), ldh,  \
-                wr, br, E, W, top, wsg, ids, wts, gate, T)
+                wr, br, E, W, top, wsg, ids, wts, gate, T, score)
   if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
   else if (dtype == B200_F16) LAUNCH(__half);
   else if (dtype == B200_F32) LAUNCH(float);
@@ -379,6 +403,12 @@ extern "C" int b200_moe_route(const void* h, int64_t ldh, const float* wr, const
 #undef LAUNCH
   B200_CHECK_LAUNCH("moe_route_kernel");
   return 0;
+}
+
+extern "C" int b200_moe_route(const void* h, int64_t ldh, const float* wr, const float* br, int E,
+                              int W, int top, const float* wsg, int* ids, float* wts, float* gate,
+                              int T, int dtype, void* stream) {
+  return b200_moe_route_scored(h, ldh, wr, br, E, W, top, wsg, ids, wts, gate, T, 0, dtype, stream);
 }
 
 extern "C" int b200_moe_align(const int* ids, int N, int E, int* offsets, int* sorted_rows,
@@ -393,15 +423,17 @@ extern "C" int b200_moe_align(const int* ids, int N, int E, int* offsets, int* s
   return 0;
 }
 
-extern "C" int b200_moe_grouped_gemm(const void* a, int64_t lda, const void* w, int64_t ldw,
-                                     int64_t w_expert_stride, const int* offsets,
-                                     const int* sorted_rows, int E, int top, int rows, int Nout, int K,
-                                     void* out, int64_t ldo, int gated, int act, int dtype,
-                                     void* stream) {
+// mode 0: plain, 1: gated, 2: one weight + activation of the (optionally row-scaled) accumulator
+extern "C" int b200_moe_grouped_gemm_mode(const void* a, int64_t lda, const void* w, int64_t ldw,
+                                          int64_t w_expert_stride, const int* offsets,
+                                          const int* sorted_rows, int E, int top, int rows, int Nout,
+                                          int K, void* out, int64_t ldo, int mode, int act,
+                                          const float* row_scale, int dtype, void* stream) {
   using namespace b200;
   if (rows == 0) return 0;
   B200_REQUIRE(a && w && offsets && sorted_rows && out, "b200_moe_grouped_gemm: null pointer");
-  B200_REQUIRE(E > 0 && top > 0 && rows > 0 && Nout > 0 && K > 0 && (act == 0 || act == 1),
+  B200_REQUIRE(E > 0 && top > 0 && rows > 0 && Nout > 0 && K > 0 && act >= 0 && act <= 2 && mode >= 0 &&
+                   mode <= 2,
                "b200_moe_grouped_gemm: bad sizes");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   ScopedKernelTimer timer("moe_grouped_gemm", st);
@@ -410,33 +442,35 @@ extern "C" int b200_moe_grouped_gemm(const void* a, int64_t lda, const void* w, 
     // 128-row tiles once the experts average two of them; every expert can leave one partly filled tile
     const int tm = rows >= 256 * E ? 128 : 64;
     const dim3 tgrid(ceil_div(rows, tm) + min(E, rows), ceil_div(Nout, kTN));
-    const size_t smem = static_cast<size_t>(2 * tm + 2 * (gated ? 2 : 1) * kTN) * kTLd * 2;
+    const size_t smem = static_cast<size_t>(2 * tm + 2 * (mode == 1 ? 2 : 1) * kTN) * kTLd * 2;
 #define LAUNCH_TM(TT, G, TMV)                                                                        \
   do {                                                                                               \
     auto kern = moe_grouped_gemm_mma_kernel<TT, G, TMV>;                                             \
     if (smem > 48 * 1024)                                                                            \
       B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,           \
                                         static_cast<int>(smem)));                                    \
-    launch_kernel(kern, tgrid, dim3(128), smem, st, 1, 0, static_cast<const TT*>(a), lda,        \
+    launch_kernel(kern, tgrid, dim3(128), smem, st, 1, 0, static_cast<const TT*>(a), lda,            \
                   static_cast<const TT*>(w), ldw, w_expert_stride, offsets, sorted_rows, E, top,     \
-                  Nout, K, static_cast<TT*>(out), ldo, act);                                         \
+                  Nout, K, static_cast<TT*>(out), ldo, act, row_scale);                              \
   } while (0)
 #define LAUNCH_TC(TT, G)                                                                             \
   do {                                                                                               \
     if (tm == 128) LAUNCH_TM(TT, G, 128);                                                            \
     else LAUNCH_TM(TT, G, 64);                                                                       \
   } while (0)
-    if (dtype == B200_BF16) {
-      if (gated) LAUNCH_TC(__nv_bfloat16, true);
-      else LAUNCH_TC(__nv_bfloat16, false);
-    } else {
-      if (gated) LAUNCH_TC(__half, true);
-      else LAUNCH_TC(__half, false);
-    }
+#define BY_MODE(TT)                    \
+  do {                                 \
+    if (mode == 1) LAUNCH_TC(TT, 1);   \
+    else if (mode == 2) LAUNCH_TC(TT, 2); \
+    else LAUNCH_TC(TT, 0);             \
+  } while (0)
+    if (dtype == B200_BF16) BY_MODE(__nv_bfloat16);
+    else BY_MODE(__half);
+#undef BY_MODE
 #undef LAUNCH_TC
 #undef LAUNCH_TM
     B200_CHECK_LAUNCH("moe_grouped_gemm_mma_kernel");
-    note_variant("moe_grouped_gemm_mma gated%d", gated);
+    note_variant("moe_grouped_gemm_mma gated%d", mode);
     return 0;
   }
   // every expert can leave one partly filled row tile
@@ -444,11 +478,12 @@ extern "C" int b200_moe_grouped_gemm(const void* a, int64_t lda, const void* w, 
 #define LAUNCH(TT, G)                                                                                \
   launch_kernel(moe_grouped_gemm_kernel<TT, G>, grid, dim3(256), 0, st, 1, 0,                        \
                 static_cast<const TT*>(a), lda, static_cast<const TT*>(w), ldw, w_expert_stride,     \
-                offsets, sorted_rows, E, top, Nout, K, static_cast<TT*>(out), ldo, act)
-#define BY_G(TT)          \
-  do {                    \
-    if (gated) LAUNCH(TT, true); \
-    else LAUNCH(TT, false);      \
+                offsets, sorted_rows, E, top, Nout, K, static_cast<TT*>(out), ldo, act, row_scale)
+#define BY_G(TT)                     \
+  do {                               \
+    if (mode == 1) LAUNCH(TT, 1);    \
+    else if (mode == 2) LAUNCH(TT, 2); \
+    else LAUNCH(TT, 0);              \
   } while (0)
   if (dtype == B200_BF16) BY_G(__nv_bfloat16);
   else if (dtype == B200_F16) BY_G(__half);
@@ -458,4 +493,13 @@ extern "C" int b200_moe_grouped_gemm(const void* a, int64_t lda, const void* w, 
 #undef LAUNCH
   B200_CHECK_LAUNCH("moe_grouped_gemm_kernel");
   return 0;
+}
+
+extern "C" int b200_moe_grouped_gemm(const void* a, int64_t lda, const void* w, int64_t ldw,
+                                     int64_t w_expert_stride, const int* offsets,
+                                     const int* sorted_rows, int E, int top, int rows, int Nout, int K,
+                                     void* out, int64_t ldo, int gated, int act, int dtype,
+                                     void* stream) {
+  return b200_moe_grouped_gemm_mode(a, lda, w, ldw, w_expert_stride, offsets, sorted_rows, E, top, rows,
+                                    Nout, K, out, ldo, gated ? 1 : 0, act, nullptr, dtype, stream);
 }

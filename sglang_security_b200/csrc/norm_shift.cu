@@ -7,6 +7,11 @@
 //                          position 0.  The state row is replaced by the h of the portion's last token.
 //   residual_combine     : x += a + b + sum_k w[t,k] * y[t*top+k] + g[t] * s[t]   (all terms optional)
 //   act_and_mul          : out = act(z[:, :d]) * z[:, d:]  with act = silu or the tanh form of gelu
+//   add_normed           : for designs whose norm sits on a sublayer's OUTPUT: y = sa * a + sb * b +
+//                          sum_k rows[t * top + k] (all terms optional) in fp32, then
+//                          x += mult * y / sqrt(mean(y^2) + eps) * w[d]; optionally also writes the new x
+//                          in the model dtype, the next sublayer's input
+//   softcap_rows         : out = cap * tanh(z / cap) in fp32
 #include "common.cuh"
 
 namespace b200 {
@@ -126,6 +131,47 @@ act_and_mul_kernel(const T* __restrict__ z, int64_t ldz, T* __restrict__ out, in
   }
 }
 
+template <typename TA>
+__global__ void __launch_bounds__(kRowThreads)
+add_normed_kernel(float* __restrict__ x, int64_t ldx, const TA* __restrict__ a, int64_t lda, float sa,
+                  const TA* __restrict__ b, int64_t ldb, float sb, const TA* __restrict__ y,
+                  int64_t ldy, int top, const float* __restrict__ w, float eps, float mult,
+                  TA* __restrict__ out_h, int64_t ldh, int W) {
+  __shared__ float red[kRowThreads / 32];
+  const int t = blockIdx.x;
+  auto term = [&](int d) {
+    float v = 0.f;
+    if (a) v = sa * to_float<TA>(a[t * lda + d]);
+    if (b) v = fmaf(sb, to_float<TA>(b[t * ldb + d]), v);
+    if (y)
+      for (int k = 0; k < top; ++k) v += to_float<TA>(y[(static_cast<int64_t>(t) * top + k) * ldy + d]);
+    return v;
+  };
+  float s = 0.f;
+  for (int d = threadIdx.x; d < W; d += kRowThreads) {
+    const float v = term(d);
+    s = fmaf(v, v, s);
+  }
+  s = block_sum(s, red);
+  const float r = mult / sqrtf(s / static_cast<float>(W) + eps);
+  for (int d = threadIdx.x; d < W; d += kRowThreads) {
+    const float nx = fmaf(term(d) * r, w ? w[d] : 1.f, x[t * ldx + d]);
+    x[t * ldx + d] = nx;
+    if (out_h) out_h[t * ldh + d] = from_float<TA>(nx);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+softcap_rows_kernel(const T* __restrict__ z, int64_t ldz, float* __restrict__ out, int64_t ldo, int V,
+                    float cap) {
+  const int t = blockIdx.x;
+  for (int d = threadIdx.x; d < V; d += kRowThreads) {
+    const float v = to_float<T>(z[t * ldz + d]);
+    out[t * ldo + d] = cap > 0.f ? cap * tanhf(v / cap) : v;
+  }
+}
+
 }  // namespace b200
 
 extern "C" int b200_scalar_rmsnorm_shift(const float* x, int64_t ldx, const float* gain,
@@ -195,5 +241,48 @@ extern "C" int b200_act_and_mul(const void* z, int64_t ldz, void* out, int64_t l
   else B200_REQUIRE(false, "b200_act_and_mul: dtype %d", dtype);
 #undef LAUNCH
   B200_CHECK_LAUNCH("act_and_mul_kernel");
+  return 0;
+}
+
+extern "C" int b200_add_normed(float* x, int64_t ldx, const void* a, int64_t lda, float sa,
+                               const void* b, int64_t ldb, float sb, const void* rows, int64_t ld_rows,
+                               int top, const float* w, float eps, float mult, void* out_h, int64_t ldh,
+                               int T, int W, int dtype, void* stream) {
+  using namespace b200;
+  if (T == 0) return 0;
+  B200_REQUIRE(x && (a || b || rows) && T > 0 && W > 0, "b200_add_normed: bad arguments");
+  B200_REQUIRE(!rows || top > 0, "b200_add_normed: rows without a count per token");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer("add_normed", st);
+#define LAUNCH(TA)                                                                                   \
+  launch_kernel(add_normed_kernel<TA>, dim3(T), dim3(kRowThreads), 0, st, 1, 0, x, ldx,             \
+                static_cast<const TA*>(a), lda, sa, static_cast<const TA*>(b), ldb, sb,              \
+                static_cast<const TA*>(rows), ld_rows, top, w, eps, mult, static_cast<TA*>(out_h),   \
+                ldh, W)
+  if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
+  else if (dtype == B200_F16) LAUNCH(__half);
+  else if (dtype == B200_F32) LAUNCH(float);
+  else B200_REQUIRE(false, "b200_add_normed: dtype %d", dtype);
+#undef LAUNCH
+  B200_CHECK_LAUNCH("add_normed_kernel");
+  return 0;
+}
+
+extern "C" int b200_softcap_rows(const void* z, int64_t ldz, float* out, int64_t ldo, int T, int V,
+                                 float cap, int dtype, void* stream) {
+  using namespace b200;
+  if (T == 0) return 0;
+  B200_REQUIRE(z && out && T > 0 && V > 0, "b200_softcap_rows: bad arguments");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ScopedKernelTimer timer("softcap_rows", st);
+#define LAUNCH(TT)                                                                                   \
+  launch_kernel(softcap_rows_kernel<TT>, dim3(T), dim3(kRowThreads), 0, st, 1, 0,                   \
+                static_cast<const TT*>(z), ldz, out, ldo, V, cap)
+  if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
+  else if (dtype == B200_F16) LAUNCH(__half);
+  else if (dtype == B200_F32) LAUNCH(float);
+  else B200_REQUIRE(false, "b200_softcap_rows: dtype %d", dtype);
+#undef LAUNCH
+  B200_CHECK_LAUNCH("softcap_rows_kernel");
   return 0;
 }

@@ -1,12 +1,17 @@
 """Mixture-of-experts feed-forward on the kernels of csrc/moe.cu.
 
     TopKRouter   : z = W_r h + b in fp32; the `top` largest logits; weights = softmax over the chosen
-                   logits only.  Optionally the scalar gate sigmoid(w_sg . h) of a shared expert.
+                   logits only, or (score="sigmoid") the sigmoid of each chosen logit, not
+                   renormalised.  Optionally the scalar gate sigmoid(w_sg . h) of a shared expert.
     FusedExperts : all experts' gated feed-forwards W_down (act(W_gate h) * (W_up h)) as two grouped
                    GEMMs over the (token, choice) rows sorted by expert; nothing is read back to the
                    host, so the step stays capturable.  Returns one row per (token, choice); the
                    weighted sum is taken in fp32 together with the residual add
                    (layers/scalar_norm.py residual_combine).
+    ScaledInputExperts : experts without a gate, W_down act(W_up (s h)), whose router weight s
+                   multiplies the expert's INPUT.  Same sort and grouped GEMMs; s is applied to the
+                   fp32 accumulator of the up-projection (W (s h) = s (W h)) before the activation.
+                   Returns one row per (token, choice), already weighted: the caller only sums them.
 """
 from __future__ import annotations
 
@@ -20,9 +25,14 @@ from ..activation import GatedActAndMul
 
 
 class TopKRouter(nn.Module):
-    def __init__(self, width: int, experts: int, top: int, bias: bool = True, shared_gate: bool = False):
+    SCORES = {"softmax_chosen": 0, "sigmoid": 1}
+
+    def __init__(self, width: int, experts: int, top: int, bias: bool = True, shared_gate: bool = False,
+                 score: str = "softmax_chosen"):
         super().__init__()
-        self.experts, self.top = experts, top
+        if score not in self.SCORES:
+            raise ValueError(f"unknown router score {score!r}")
+        self.experts, self.top, self.score = experts, top, self.SCORES[score]
         self.weight = nn.Parameter(torch.zeros(experts, width, dtype=torch.float32), requires_grad=False)
         self.bias = nn.Parameter(torch.zeros(experts, dtype=torch.float32), requires_grad=False) if bias else None
         self.shared_gate = (nn.Parameter(torch.zeros(width, dtype=torch.float32), requires_grad=False)
@@ -36,10 +46,10 @@ class TopKRouter(nn.Module):
         ids = torch.empty((t, self.top), dtype=torch.int32, device=h.device)
         wts = torch.empty((t, self.top), dtype=torch.float32, device=h.device)
         gate = torch.empty((t,), dtype=torch.float32, device=h.device) if self.shared_gate is not None else None
-        rc = _lib.load().b200_moe_route(
+        rc = _lib.load().b200_moe_route_scored(
             h.data_ptr(), h.stride(0), self.weight.data_ptr(), _lib.ptr(self.bias), self.experts, w,
             self.top, _lib.ptr(self.shared_gate), ids.data_ptr(), wts.data_ptr(), _lib.ptr(gate), t,
-            _lib.dtype_code(h.dtype), _lib.current_stream())
+            self.score, _lib.dtype_code(h.dtype), _lib.current_stream())
         _lib.check(rc, "b200_moe_route")
         return ids, wts, gate
 
@@ -81,4 +91,43 @@ class FusedExperts(nn.Module):
             self.w_down.stride(0), offsets.data_ptr(), sorted_rows.data_ptr(), self.experts, top, n,
             self.width, self.ff, out.data_ptr(), out.stride(0), 0, self.act_kind, code, st)
         _lib.check(rc, "b200_moe_grouped_gemm")
+        return out
+
+
+class ScaledInputExperts(nn.Module):
+    ACTS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}
+
+    def __init__(self, width: int, ff: int, experts: int, act: str = "relu2",
+                 params_dtype: torch.dtype = torch.bfloat16):
+        super().__init__()
+        if act not in self.ACTS:
+            raise ValueError(f"unknown activation {act!r}")
+        self.width, self.ff, self.experts, self.act_kind = width, ff, experts, self.ACTS[act]
+        self.w_up = nn.Parameter(torch.empty(experts, ff, width, dtype=params_dtype), requires_grad=False)
+        self.w_down = nn.Parameter(torch.empty(experts, width, ff, dtype=params_dtype), requires_grad=False)
+
+    def forward(self, h: torch.Tensor, ids: torch.Tensor, weights: Optional[torch.Tensor]) -> torch.Tensor:
+        """h [T, width], ids int32 [T, top], weights fp32 [T, top] (None: unweighted) ->
+        [T * top, width], row t * top + k = expert ids[t, k] applied to weights[t, k] * h[t]."""
+        t, top = ids.shape
+        n = t * top
+        lib, st, code = _lib.load(), _lib.current_stream(), _lib.dtype_code(h.dtype)
+        dev = h.device
+        offsets = torch.empty(self.experts + 1, dtype=torch.int32, device=dev)
+        sorted_rows = torch.empty(n, dtype=torch.int32, device=dev)
+        rc = lib.b200_moe_align(ids.data_ptr(), n, self.experts, offsets.data_ptr(),
+                                sorted_rows.data_ptr(), st)
+        _lib.check(rc, "b200_moe_align")
+        inter = torch.empty((n, self.ff), dtype=h.dtype, device=dev)
+        rc = lib.b200_moe_grouped_gemm_mode(
+            h.data_ptr(), h.stride(0), self.w_up.data_ptr(), self.w_up.stride(1), self.w_up.stride(0),
+            offsets.data_ptr(), sorted_rows.data_ptr(), self.experts, top, n, self.ff, self.width,
+            inter.data_ptr(), inter.stride(0), 2, self.act_kind, _lib.ptr(weights), code, st)
+        _lib.check(rc, "b200_moe_grouped_gemm_mode")
+        out = torch.empty((n, self.width), dtype=h.dtype, device=dev)
+        rc = lib.b200_moe_grouped_gemm_mode(
+            inter.data_ptr(), inter.stride(0), self.w_down.data_ptr(), self.w_down.stride(1),
+            self.w_down.stride(0), offsets.data_ptr(), sorted_rows.data_ptr(), self.experts, top, n,
+            self.width, self.ff, out.data_ptr(), out.stride(0), 0, self.act_kind, None, code, st)
+        _lib.check(rc, "b200_moe_grouped_gemm_mode")
         return out

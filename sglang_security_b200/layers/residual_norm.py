@@ -1,0 +1,65 @@
+"""Norm on a sublayer's OUTPUT followed by the residual add, for designs whose sublayers read the
+32-bit residual itself (csrc/norm_shift.cu add_normed):
+
+    y = sa * a + sb * b + sum_k rows[t * top + k]        (fp32 sum of the terms given)
+    x += mult * y / sqrt(mean(y^2) + eps) * weight
+
+`AddNormed` owns the weight; one launch does the sum, the norm, the add and, on request, the copy of
+the new residual in the model dtype that the next sublayer's matrix products read.  `softcap` is the
+logit cap cap * tanh(z / cap) with a fp32 result."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from .. import _lib
+
+
+class AddNormed(nn.Module):
+    def __init__(self, width: int, eps: float, mult: float = 1.0):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(width, dtype=torch.float32), requires_grad=False)
+        self.eps, self.mult = float(eps), float(mult)
+
+    def forward(self, x: torch.Tensor, a: Optional[torch.Tensor] = None, sa: float = 1.0,
+                b: Optional[torch.Tensor] = None, sb: float = 1.0, rows: Optional[torch.Tensor] = None,
+                top: int = 0, out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+        """x: fp32 residual [T, W], updated in place.  -> the new x in `out_dtype` (None: not asked)."""
+        if not x.is_cuda:
+            raise _lib.B200Error("AddNormed: tensor must live on a CUDA device (no CPU path)")
+        if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1:
+            raise _lib.B200Error("AddNormed: the residual must be a 2-D fp32 tensor with contiguous rows")
+        terms = [v for v in (a, b, rows) if v is not None]
+        if not terms:
+            raise _lib.B200Error("AddNormed: nothing to add")
+        dt = terms[0].dtype
+        for v in terms:
+            if v.dtype != dt or v.stride(-1) != 1:
+                raise _lib.B200Error("AddNormed: terms must share a dtype and have contiguous rows")
+        t, w = x.shape
+        out = None
+        if out_dtype is not None and out_dtype != torch.float32:
+            if out_dtype != dt:
+                raise _lib.B200Error("AddNormed: the copy of the residual has the terms' dtype")
+            out = torch.empty((t, w), dtype=out_dtype, device=x.device)
+        ld = lambda v: v.stride(0) if v is not None else 0
+        rc = _lib.load().b200_add_normed(
+            x.data_ptr(), x.stride(0), _lib.ptr(a), ld(a), float(sa), _lib.ptr(b), ld(b), float(sb),
+            _lib.ptr(rows), ld(rows), int(top), self.weight.data_ptr(), self.eps, self.mult,
+            _lib.ptr(out), ld(out), t, w, _lib.dtype_code(dt), _lib.current_stream())
+        _lib.check(rc, "b200_add_normed")
+        return x if out_dtype == torch.float32 else out
+
+
+def softcap(z: torch.Tensor, cap: float) -> torch.Tensor:
+    """-> fp32 cap * tanh(z / cap) (cap <= 0: a fp32 copy)."""
+    if not z.is_cuda or z.dim() != 2 or z.stride(1) != 1:
+        raise _lib.B200Error("softcap: a 2-D CUDA tensor with contiguous rows is expected")
+    out = torch.empty(z.shape, dtype=torch.float32, device=z.device)
+    rc = _lib.load().b200_softcap_rows(z.data_ptr(), z.stride(0), out.data_ptr(), out.stride(0),
+                                       z.shape[0], z.shape[1], float(cap), _lib.dtype_code(z.dtype),
+                                       _lib.current_stream())
+    _lib.check(rc, "b200_softcap_rows")
+    return out

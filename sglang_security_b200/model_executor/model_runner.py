@@ -35,7 +35,7 @@ class ModelRunner:
         self.context_length = context_length or self.max_total_tokens
         self.max_running_requests = max_running_requests
         spec = self.model.cache_spec()
-        if spec.kind != "latent":
+        if spec.kind not in ("latent", "rows"):
             raise ValueError(f"cache kind {spec.kind!r} is not served by this runner")
         self.req_to_token_pool = ReqToTokenPool(max_running_requests, self.context_length, device)
         self.token_to_kv_pool = LatentTokenToKVPool(self.max_total_tokens, page_size, dtype,

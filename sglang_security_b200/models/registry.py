@@ -17,8 +17,9 @@ _MODELS: Dict[str, Type] = {}
 
 @dataclass
 class CacheSpec:
-    kind: str                                   # "latent" (one row per token) | "mha"
-    row_dims: Dict[int, int] = field(default_factory=dict)     # owning layer -> row width
+    kind: str                                   # "latent" / "rows": one row per token and owning layer
+    row_dims: Dict[int, int] = field(default_factory=dict)     # owning layer -> row width (layers
+                                                               # without an entry cache nothing per token)
     source_of: Dict[int, int] = field(default_factory=dict)    # layer -> layer whose rows it reads
     state_widths: Dict[int, int] = field(default_factory=dict)  # layer -> fp32 carry width per sequence
 
@@ -31,7 +32,7 @@ def register_model(architecture: str):
 
 
 def resolve_model_cls(architecture: str):
-    from . import desirax  # noqa: F401  (registers itself)
+    from . import desirax, dozetar  # noqa: F401  (register themselves)
 
     if architecture not in _MODELS:
         raise ValueError(f"architecture {architecture!r} is not supported; known: {sorted(_MODELS)}")
@@ -39,6 +40,6 @@ def resolve_model_cls(architecture: str):
 
 
 def supported_architectures():
-    from . import desirax  # noqa: F401
+    from . import desirax, dozetar  # noqa: F401
 
     return sorted(_MODELS)
