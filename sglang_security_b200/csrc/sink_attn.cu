@@ -105,7 +105,7 @@ qk_norm_rope_write_kernel(const T* __restrict__ q, int64_t ldq, const T* __restr
     const int group = is_q ? q_group : k_group;
     float x = normed(row, i, w, inv, group);
     if (d < rot_dims) {
-      const float y = normed(row, i ^ 1, w, inv, group);   // D and rot_dims are even: the pair stays in the head
+      const float y = normed(row, i - d + (d ^ 1), w, inv, group);   // rot_dims is even: the pair stays in the head
       const float c = cs[d >> 1], s = sn[d >> 1];
       x = (d & 1) ? fmaf(x, c, y * s) : fmaf(x, c, -y * s);
     }
@@ -245,7 +245,7 @@ extern "C" int b200_qk_norm_rope_write(const void* q, int64_t ldq, const void* k
   if (T == 0) return 0;
   B200_REQUIRE(q && k && v && tok_pos && loc && pool && q_out, "b200_qk_norm_rope_write: null pointer");
   B200_REQUIRE(T > 0 && H > 0 && G > 0 && D > 0 && E > 0 && rot_dims >= 0 && rot_dims <= D &&
-                   rot_dims % 2 == 0 && (rot_dims == 0 || (freq_hi && D % 2 == 0)),
+                   rot_dims % 2 == 0 && (rot_dims == 0 || freq_hi),
                "b200_qk_norm_rope_write: head size %d, rotated %d", D, rot_dims);
   B200_REQUIRE((q_group == 0 || (H * D) % q_group == 0) && (k_group == 0 || (G * D) % k_group == 0) &&
                    q_group >= 0 && k_group >= 0,

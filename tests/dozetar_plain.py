@@ -103,17 +103,28 @@ def sink_attention(h, w, p: str, a: dict, eps: float):
         q = rotate_pairs(q, pos, int(rot["dims"]), float(rot["base"]))
         k = rotate_pairs(k, pos, int(rot["dims"]), float(rot["base"]))
     mask = a.get("mask") or {}
-    ok = visible(T, mask.get("size"), int(mask.get("keep_first", 0)))
+    out = sink_softmax(q, k, v, float(a["scale"]), mask.get("size"), int(mask.get("keep_first", 0)),
+                       _f(w[p + "sink"]))
+    return lin(out.reshape(T, H * E), w[p + "o"], w[p + "o.b"])
+
+
+def sink_softmax(q, k, v, scale: float, size: Optional[int], keep_first: int,
+                 sink: Optional[torch.Tensor]) -> torch.Tensor:
+    """q [T, H, D], k [T, G, D], v [T, G, E] of ONE sequence from position 0 -> [T, H, E].  exp(sink_h)
+    joins the denominator only."""
+    T, H, _ = q.shape
+    G, E = k.shape[1], v.shape[-1]
+    ok = visible(T, size, keep_first)
     out = torch.zeros(T, H, E, dtype=DT)
-    sink = _f(w[p + "sink"])
     for hd in range(H):
         g = hd // (H // G)
-        s = (q[:, hd] @ k[:, g].t()) * float(a["scale"])
+        s = (q[:, hd] @ k[:, g].t()) * scale
         s = s.masked_fill(~ok, -math.inf)
-        top = torch.maximum(s.max(-1).values, sink[hd])
+        top = s.max(-1).values if sink is None else torch.maximum(s.max(-1).values, sink[hd])
         e = torch.exp(s - top[:, None])
-        out[:, hd] = (e @ v[:, g]) / (e.sum(-1) + torch.exp(sink[hd] - top))[:, None]
-    return lin(out.reshape(T, H * E), w[p + "o"], w[p + "o.b"])
+        den = e.sum(-1) if sink is None else e.sum(-1) + torch.exp(sink[hd] - top)
+        out[:, hd] = (e @ v[:, g]) / den[:, None]
+    return out
 
 
 def decayed_recurrence(q, k, v, decay):

@@ -1,0 +1,179 @@
+"""Dozetar through the engine (loader, ModelRunner, pools, scheduler) against the plain restatement:
+whole prompts, per-layer residuals, token-by-token decoding, portions down to two tokens, unequal
+requests in one batch with pages and request slots freed and used again, edges made visible by a
+peaked softmax, long decoding, and greedy generation through Engine.generate."""
+import pytest
+import torch
+
+import dozetar_plain as P
+import dozetar_util as U
+
+pytestmark = pytest.mark.gpu
+
+CONFIGS = {
+    # recurrent layers around a parallel one; experts top 2
+    "a": lambda: U.config([(U.mlstm(), U.experts(5, 2, 24)), (U.parallel(), U.experts(5, 2, 24)),
+                           (U.mlstm(), U.experts(5, 2, 24)), (U.parallel(window=20, keep_first=3), None)]),
+    # other sizes: parallel first, one key/value head per query head, rotation of the whole head, no kept
+    # tokens, a layer without feed-forward, top 1, no logit cap, sizes that are no multiples of 8
+    "b": lambda: U.config([(U.parallel(heads=3, kv_heads=3, dim=10, vdim=6, window=70, keep_first=0, rot_dims=10,
+                                       base=500.0, r_heads=1, r_dim=33, r_vdim=7, decay=[0.97]), U.experts(9, 1, 40)),
+                           (U.mlstm(heads=1, dim=50, vdim=70, cap=15.0), None),
+                           (U.parallel(heads=2, kv_heads=1, dim=32, vdim=32, window=None, rot_dims=0, r_heads=2,
+                                       r_dim=8, r_vdim=8), U.experts(3, 3, 16))],
+                          vocab=131, width=72, eps=1e-3, mult=1.0, softcap=None),
+    # windows of one and two tokens, more kept tokens than the window, one head everywhere
+    "c": lambda: U.config([(U.parallel(heads=1, kv_heads=1, dim=8, vdim=8, window=1, keep_first=0, rot_dims=2,
+                                       r_heads=1, r_dim=4, r_vdim=4), U.experts(2, 1, 8)),
+                           (U.parallel(heads=1, kv_heads=1, dim=8, vdim=8, window=2, keep_first=5, rot_dims=4,
+                                       r_heads=1, r_dim=4, r_vdim=4), None),
+                           (U.mlstm(heads=1, dim=4, vdim=4, cap=3.0), None)], vocab=33, width=24, mult=0.3),
+}
+
+
+def _model(tmp_path, name, seed=0, sharp=False):
+    cfg = CONFIGS[name]()
+    if sharp:        # a peaked softmax: one key more or less inside a window moves the logits a lot
+        for L in cfg["layers"]:
+            if L["type"] == "parallel":
+                L["mixer"]["left"]["scale"] *= 6.0
+    w = U.random_weights(cfg, seed)
+    return cfg, w, U.write_model(str(tmp_path / name), cfg, w)
+
+
+def _tokens(cfg, n, seed):
+    return torch.randint(0, cfg["vocab"], (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+TOL = {torch.float32: 1e-4, torch.bfloat16: 6e-2}
+TOL_SHARP = {torch.float32: 1e-4, torch.bfloat16: 0.15}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_whole_prompt_matches_plain_model(tmp_path, name, dtype):
+    cfg, w, folder = _model(tmp_path, name)
+    toks = _tokens(cfg, 150, 1)
+    want = P.forward(cfg, w, toks)
+    d = U.Driver(folder, dtype)
+    d.step([("r", toks)], end=["r"])
+    assert U.rel_err(d.result("r"), want, dtype) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_layer_outputs_match_plain_model_fp32(tmp_path, name):
+    from sglang_security_b200.managers.schedule_batch import Req, StepItem
+
+    cfg, w, folder = _model(tmp_path, name)
+    toks = _tokens(cfg, 40, 2)
+    want = []
+    P.forward(cfg, w, toks, layer_outputs=want)
+    d = U.Driver(folder, torch.float32)
+    req = Req(rid="x", input_ids=list(toks))
+    d.runner.admit(req)
+    got = []
+    d.sched.run_step([StepItem(req, list(toks), want=[0])], layer_hook=lambda i, x: got.append(x.double().cpu().clone()))
+    assert len(got) == len(want)
+    for g, t in zip(got, want):
+        assert (g - t).abs().max() <= 2e-5 * t.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_prefill_then_token_by_token(tmp_path, name, dtype):
+    cfg, w, folder = _model(tmp_path, name, sharp=True)
+    toks = _tokens(cfg, 130, 3)
+    want = P.forward(cfg, w, toks)
+    d = U.Driver(folder, dtype)
+    d.step([("r", toks[:60])])
+    for t in toks[60:]:
+        d.step([("r", [t])])
+    assert U.rel_err(d.result("r"), want, dtype) <= TOL_SHARP[dtype]
+    d2 = U.Driver(folder, dtype)                 # from the very first token on, one at a time
+    for t in toks[:40]:
+        d2.step([("s", [t])])
+    assert U.rel_err(d2.result("s"), want[:40], dtype) <= TOL_SHARP[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sizes", [[2], [3, 64, 2, 17, 1], [64, 5]])
+def test_portions_of_a_prompt(tmp_path, dtype, sizes):
+    cfg, w, folder = _model(tmp_path, "a", sharp=True)
+    toks = _tokens(cfg, 140, 4)
+    want = P.forward(cfg, w, toks)
+    d = U.Driver(folder, dtype)
+    at = 0
+    for n in U.cut(len(toks), sizes):
+        d.step([("r", toks[at:at + n])])
+        at += n
+    assert U.rel_err(d.result("r"), want, dtype) <= TOL_SHARP[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_unequal_requests_in_one_batch_with_slots_and_pages_reused(tmp_path, name, dtype):
+    cfg, w, folder = _model(tmp_path, name)
+    lens = {"p": 150, "q": 37, "r": 90, "s": 1, "t": 64, "u": 129, "v": 20}
+    toks = {k: _tokens(cfg, n, 10 + i) for i, (k, n) in enumerate(lens.items())}
+    want = {k: P.forward(cfg, w, t) for k, t in toks.items()}
+    d = U.Driver(folder, dtype, max_tokens=512, max_requests=3)      # fewer slots and pages than requests need
+    at = {k: 0 for k in lens}
+    waiting, live, sizes, step = list(lens), [], [33, 1, 2, 64, 1, 7], 0
+    while waiting or live:
+        while waiting and len(live) < 3 and sum(-(-lens[k] // 64) for k in live + [waiting[0]]) <= 8:
+            live.append(waiting.pop(0))
+        portions, ended = [], []
+        for j, k in enumerate(live):
+            n = min(sizes[(step + j) % len(sizes)], lens[k] - at[k])
+            portions.append((k, toks[k][at[k]:at[k] + n]))
+            at[k] += n
+            if at[k] == lens[k]:
+                ended.append(k)
+        d.step(portions, end=ended)
+        live = [k for k in live if k not in ended]
+        step += 1
+    for k in lens:
+        assert U.rel_err(d.result(k), want[k], dtype) <= TOL[dtype], k
+    assert d.runner.free_token_slots() == d.runner.max_total_tokens
+
+
+def test_batch_does_not_change_a_request_fp32(tmp_path):
+    cfg, w, folder = _model(tmp_path, "a")
+    a, b = _tokens(cfg, 80, 20), _tokens(cfg, 45, 21)
+    alone = U.Driver(folder, torch.float32)
+    alone.step([("a", a)], end=["a"])
+    both = U.Driver(folder, torch.float32)
+    both.step([("b", b[:30]), ("a", a[:50])])
+    both.step([("a", a[50:]), ("b", b[30:31])])
+    assert (alone.result("a") - both.result("a")).abs().max() <= 1e-4
+
+
+def test_long_decoding(tmp_path):
+    cfg, w, folder = _model(tmp_path, "a")
+    toks = _tokens(cfg, 430, 5)
+    want = P.forward(cfg, w, toks)
+    d = U.Driver(folder, torch.float32)
+    d.step([("r", toks[:30])])
+    for t in toks[30:]:
+        d.step([("r", [t])])
+    assert U.rel_err(d.result("r"), want) <= 1e-4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_greedy_generation_through_the_engine(tmp_path, dtype):
+    from sglang_security_b200.entrypoints.engine import Engine
+    from sglang_security_b200.managers.schedule_batch import SamplingParams
+
+    cfg, w, folder = _model(tmp_path, "a")
+    prompts = [_tokens(cfg, n, 30 + i) for i, n in enumerate([70, 9, 130, 33, 2])]     # more requests than slots
+    eng = Engine(folder, dtype, max_total_tokens=1024, max_running_requests=3, chunked_prefill_size=48)
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=12))
+    assert eng.runner.free_token_slots() == eng.runner.max_total_tokens
+    for p, o in zip(prompts, outs):
+        assert len(o) == 12
+        logits = P.forward(cfg, w, p + o[:-1])[len(p) - 1:]
+        # teacher-forced: every generated token is (within rounding) the oracle's best token there
+        best = logits.max(-1).values
+        took = logits[torch.arange(len(o)), torch.tensor(o)]
+        slack = 1e-3 if dtype == torch.float32 else 0.15
+        assert ((best - took) <= slack * logits.std(-1)).all()
