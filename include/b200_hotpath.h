@@ -238,6 +238,16 @@ int b200_attn_extend_window(const void* q, int64_t q_stride, const void* k_cache
                             const int32_t* extend_start_loc, int bs, int max_extend_len, int Hq,
                             int Hkv, int D, int Dv, float scale, float logit_cap, float out_scale,
                             int causal, int window, int dtype, void* stream);
+/* Same kernel with a window that also keeps the first keep_first keys of the sequence visible, and an
+ * optional sink per query head (fp32 [Hq]): exp(sink[h]) joins the softmax denominator.            */
+int b200_attn_extend_sink(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                          int64_t kv_row_stride, void* o, int64_t o_stride,
+                          const int32_t* req_to_token, int64_t req_to_token_stride,
+                          const int64_t* req_pool_indices, const int64_t* seq_lens,
+                          const int32_t* extend_prefix_lens, const int32_t* extend_seq_lens,
+                          const int32_t* extend_start_loc, int bs, int max_extend_len, int Hq, int Hkv,
+                          int D, int Dv, float scale, float logit_cap, float out_scale, int causal,
+                          int window, int keep_first, const float* sink, int dtype, void* stream);
 /* FP8 (e4m3) pool -> dense 16-bit rows for the extend kernel (prefill is compute-bound; the extra
  * pass costs 3 bytes/element once per layer): for request b and t < seq_lens[b]
  *   k_out[kv_indptr[b] + t, :] = exact(k_cache[slot(b,t), :]),  dense_rtt[b, t] = kv_indptr[b] + t
@@ -638,22 +648,24 @@ int b200_gated_group_rmsnorm(const float* o, int64_t ldo, const float* w, const 
 
 /* Attention with a sink, step 1: q (H heads) and k (G heads) of size D are RMS-normed in groups of
  * q_group / k_group coordinates (0 = no norm) with weights qw / kw, rotated (interleaved pairs, first
- * rot_dims coordinates, angle = position * (freq_hi + freq_lo)); queries go to q_out (fp32), keys to
- * pool[loc[t]][k_off ...], values (G heads of size E) to pool[loc[t]][v_off ...].                 */
+ * rot_dims coordinates, angle = position * (freq_hi + freq_lo)); queries go to q_out (fp32) and / or
+ * q_out16 (the model dtype), keys to pool[loc[t]][k_off ...], values (G heads of size E) to
+ * pool[loc[t]][v_off ...].                                                                        */
 int b200_qk_norm_rope_write(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
                             int64_t ldv, const float* qw, const float* kw, int q_group, int k_group,
                             float eps, const float* freq_hi, const float* freq_lo, int rot_dims,
                             const int* tok_pos, const int64_t* loc, void* pool, int64_t ld_pool,
-                            int k_off, int v_off, float* q_out, int64_t ldqo, int T, int H, int G,
-                            int D, int E, int dtype, void* stream);
+                            int k_off, int v_off, float* q_out, int64_t ldqo, void* q_out16,
+                            int64_t ldqo16, int T, int H, int G, int D, int E, int dtype, void* stream);
 /* Step 2: token t at position p of request req_idx[tok_b[t]] sees keys j <= p with p - j < window
  * (window 0: all) or j < keep_first; weights = exp(score) / (sum exp(score) + exp(sink[h])) (sink
- * NULL: plain softmax); out [T, H * E] in the pool's dtype.                                        */
+ * NULL: plain softmax); out [T, H * E] in the pool's dtype.  With tok_list (T row numbers) only
+ * those rows of q / out are done.                                                                  */
 int b200_sink_attn(const float* q, int64_t ldq, const void* pool, int64_t ld_pool, int k_off,
                    int v_off, const int* req_to_token, int64_t ld_r2t, const int64_t* req_idx,
                    const int* tok_pos, const int* tok_b, const float* sink, float scale, int window,
-                   int keep_first, void* out, int64_t ldo, int T, int H, int G, int D, int E, int dtype,
-                   void* stream);
+                   int keep_first, void* out, int64_t ldo, int T, int H, int G, int D, int E,
+                   const int* tok_list, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

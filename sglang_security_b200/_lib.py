@@ -175,6 +175,11 @@ _SIGNATURES = {
                                         c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                         c_float, c_float, c_float, c_int, c_int, c_int, c_void_p]),
+    "b200_attn_extend_sink": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p,
+                                      c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                      c_float, c_float, c_float, c_int, c_int, c_int, c_void_p, c_int,
+                                      c_void_p]),
     "b200_moe_route": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "b200_moe_align": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
@@ -201,10 +206,11 @@ _SIGNATURES = {
     "b200_qk_norm_rope_write": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
                                         c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_int,
                                         c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
-                                        c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+                                        c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
+                                        c_void_p]),
     "b200_sink_attn": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_int64,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p,
-                               c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+                               c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
 }
 
 

@@ -48,6 +48,8 @@ struct ExtendParams {
   float out_scale;               // output multiplier (v_scale of an FP8 KV pool; 1 otherwise)
   int causal;
   int window;                    // causal sliding window: row at position i sees i - window < j <= i (0 = all)
+  int keep_first;                // with a window: keys j < keep_first stay visible outside it
+  const float* sink;             // [Hq] or NULL: exp(sink[h]) joins the softmax denominator, no key or value
 };
 
 constexpr int kExtThreads = 256;
@@ -119,7 +121,11 @@ attn_extend_kernel(const ExtendParams p) {
   // sliding window: the tiles before the first key any row of this CTA sees are skipped; loop
   // index j stands for key tile j + jb
   const int jb = (p.causal && p.window > 0) ? max(0, prefix + tok0 - p.window + 1) / kKvTile : 0;
-  const int n_kv = n_kv_all - jb;
+  // kept first tokens: their n_first leading tiles run before tile jb; loop index j stands for key
+  // tile tile_of(j)
+  const int n_first = (jb > 0 && p.keep_first > 0) ? min(ceil_div(p.keep_first, kKvTile), jb) : 0;
+  const int n_kv = n_kv_all - jb + n_first;
+  auto tile_of = [&](int j) { return j < n_first ? j : j - n_first + jb; };
   const int64_t q_row0 = p.extend_start[b];
 
   // ---- barriers ----------------------------------------------------------------------------
@@ -181,7 +187,7 @@ attn_extend_kernel(const ExtendParams p) {
     auto load_slots = [&](int j) {
 #pragma unroll
       for (int i = 0; i < PASSES; ++i) {
-        const int pos = (j + jb) * kKvTile + lrow + RPP * i;
+        const int pos = tile_of(j) * kKvTile + lrow + RPP * i;
         slots[i] = (lrow + RPP * i < kKvTile && pos < kv_len) ? __ldg(rtt + pos) : 0;  // 0 = dummy row
       }
     };
@@ -268,6 +274,7 @@ attn_extend_kernel(const ExtendParams p) {
     const bool row_ok = tok < ext;
     const int limit = p.causal ? prefix + min(tok, ext - 1) : kv_len - 1;  // last visible key
     const int first = (p.causal && p.window > 0) ? limit - p.window + 1 : 0;  // first visible key
+    const int kept = (p.causal && p.window > 0) ? p.keep_first : 0;           // keys below stay visible
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     const uint32_t tmem_s = tmem_base + lane_addr, tmem_o = tmem_base + lane_addr + C::O_COL;
     const bool capped = p.logit_cap > 0.f;
@@ -278,7 +285,7 @@ attn_extend_kernel(const ExtendParams p) {
     auto score = [&](uint32_t raw, int kpos) -> float {
       float s = __uint_as_float(raw) * p.qk_scale;
       if (capped) s = cap_log2 * fast_tanh(s * inv_cap);
-      return (kpos <= limit && kpos >= first) ? s : -INFINITY;
+      return (kpos <= limit && (kpos >= first || kpos < kept)) ? s : -INFINITY;
     };
 
     for (int j = 0; j < n_kv; ++j) {
@@ -294,13 +301,15 @@ attn_extend_kernel(const ExtendParams p) {
       tc::mbar_arrive(bar_s_free);
       float mt = -INFINITY;
       if constexpr (FAST) {
-        const int k0 = (j + jb) * kKvTile;
+        const int k0 = tile_of(j) * kKvTile;
         if (k0 + kKvTile - 1 > limit || k0 < first) {  // the tile crosses an edge of this row's visible keys
 #pragma unroll
           for (int h = 0; h < 2; ++h)
 #pragma unroll
-            for (int c = 0; c < 32; ++c)
-              if (k0 + h * 32 + c > limit || k0 + h * 32 + c < first) v[h][c] = 0xff800000u;  // -inf
+            for (int c = 0; c < 32; ++c) {
+              const int kp = k0 + h * 32 + c;
+              if (kp > limit || (kp < first && kp >= kept)) v[h][c] = 0xff800000u;  // -inf
+            }
         }
         float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
 #pragma unroll
@@ -318,7 +327,7 @@ attn_extend_kernel(const ExtendParams p) {
         for (int h = 0; h < 2; ++h)
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
-            const float sc = score(v[h][c], (j + jb) * kKvTile + h * 32 + c);
+            const float sc = score(v[h][c], tile_of(j) * kKvTile + h * 32 + c);
             v[h][c] = __float_as_uint(sc);
             mt = fmaxf(mt, sc);
           }
@@ -399,6 +408,8 @@ attn_extend_kernel(const ExtendParams p) {
     // ---- epilogue: O / l -> out
     tc::mbar_wait(bar_pv_full, (n_kv - 1) & 1u);
     tc::tc_fence_after();
+    if (p.sink && m != -INFINITY)   // m and the exponents are in log2 units
+      l += fast_exp2(p.sink[head_base + r % p.pack] * 1.4426950408889634f - m);
     const float inv_l = l > 0.f ? p.out_scale / l : 0.f;
     T* orow = static_cast<T*>(p.o) + (q_row0 + (row_ok ? tok : 0)) * p.o_stride +
               static_cast<int64_t>(head_base + r % p.pack) * D;
@@ -510,7 +521,23 @@ int b200_attn_extend_window(const void* q, int64_t q_stride, const void* k_cache
                             const int32_t* extend_start_loc, int bs, int max_extend_len, int Hq,
                             int Hkv, int D, int Dv, float scale, float logit_cap, float out_scale,
                             int causal, int window, int dtype, void* stream) {
+  return b200_attn_extend_sink(q, q_stride, k_cache, v_cache, kv_row_stride, o, o_stride, req_to_token,
+                               req_to_token_stride, req_pool_indices, seq_lens, extend_prefix_lens,
+                               extend_seq_lens, extend_start_loc, bs, max_extend_len, Hq, Hkv, D, Dv,
+                               scale, logit_cap, out_scale, causal, window, 0, nullptr, dtype, stream);
+}
+
+int b200_attn_extend_sink(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                          int64_t kv_row_stride, void* o, int64_t o_stride,
+                          const int32_t* req_to_token, int64_t req_to_token_stride,
+                          const int64_t* req_pool_indices, const int64_t* seq_lens,
+                          const int32_t* extend_prefix_lens, const int32_t* extend_seq_lens,
+                          const int32_t* extend_start_loc, int bs, int max_extend_len, int Hq, int Hkv,
+                          int D, int Dv, float scale, float logit_cap, float out_scale, int causal,
+                          int window, int keep_first, const float* sink, int dtype, void* stream) {
   using namespace b200;
+  B200_REQUIRE(keep_first >= 0 && (!sink || logit_cap <= 0.f),
+               "b200_attn_extend: kept tokens %d; a sink excludes logit capping", keep_first);
   B200_REQUIRE(window >= 0 && (window == 0 || causal), "b200_attn_extend: a window needs causal");
   if (bs == 0 || max_extend_len == 0) return 0;
   B200_REQUIRE(q && k_cache && v_cache && o && req_to_token && req_pool_indices && seq_lens &&
@@ -553,6 +580,8 @@ int b200_attn_extend_window(const void* q, int64_t q_stride, const void* k_cache
   p.qk_scale = logit_cap > 0.f ? scale : scale * 1.4426950408889634f;
   p.causal = causal;
   p.window = window;
+  p.keep_first = window > 0 ? keep_first : 0;
+  p.sink = sink;
   B200_REQUIRE(bs <= 65535 && Hkv * p.head_tiles <= 65535, "b200_attn_extend: grid too large");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == B200_BF16)

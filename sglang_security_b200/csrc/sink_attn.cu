@@ -70,8 +70,8 @@ qk_norm_rope_write_kernel(const T* __restrict__ q, int64_t ldq, const T* __restr
                           const float* __restrict__ freq_hi, const float* __restrict__ freq_lo,
                           int rot_dims, const int* __restrict__ tok_pos,
                           const int64_t* __restrict__ loc, TP* __restrict__ pool, int64_t ld_pool,
-                          int k_off, int v_off, float* __restrict__ q_out, int64_t ldqo, int H, int G,
-                          int D, int E) {
+                          int k_off, int v_off, float* __restrict__ q_out, int64_t ldqo,
+                          T* __restrict__ q_out16, int64_t ldqo16, int H, int G, int D, int E) {
   extern __shared__ float prep_smem[];       // [rot_dims / 2] cos, [rot_dims / 2] sin, group scales
   __shared__ float red[kPrepThreads / 32];
   const int t = blockIdx.x, half = rot_dims / 2;
@@ -109,8 +109,12 @@ qk_norm_rope_write_kernel(const T* __restrict__ q, int64_t ldq, const T* __restr
       const float c = cs[d >> 1], s = sn[d >> 1];
       x = (d & 1) ? fmaf(x, c, y * s) : fmaf(x, c, -y * s);
     }
-    if (is_q) q_out[t * ldqo + i] = x;
-    else prow[k_off + i] = from_float<TP>(x);
+    if (is_q) {
+      if (q_out) q_out[t * ldqo + i] = x;
+      if (q_out16) q_out16[t * ldqo16 + i] = from_float<T>(x);
+    } else {
+      prow[k_off + i] = from_float<TP>(x);
+    }
   }
   const T* vr = v + t * ldv;
   for (int i = threadIdx.x; i < G * E; i += kPrepThreads)
@@ -126,13 +130,14 @@ sink_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __restrict_
                  int64_t ld_pool, int k_off, int v_off, const int* __restrict__ req_to_token,
                  int64_t ld_r2t, const int64_t* __restrict__ req_idx, const int* __restrict__ tok_pos,
                  const int* __restrict__ tok_b, const float* __restrict__ sink, float scale, int window,
-                 int keep_first, TO* __restrict__ out, int64_t ldo, int H, int G, int D, int E) {
+                 int keep_first, TO* __restrict__ out, int64_t ldo, int H, int G, int D, int E,
+                 const int* __restrict__ tok_list) {
   extern __shared__ float sink_smem[];       // q [D], then per warp: acc [E], m, l
   float* qs = sink_smem;
   float* wacc = qs + D;
   float* wm = wacc + kSinkWarps * E;
   float* wl = wm + kSinkWarps;
-  const int t = blockIdx.x, h = blockIdx.y, g = h / (H / G);
+  const int t = tok_list ? tok_list[blockIdx.x] : blockIdx.x, h = blockIdx.y, g = h / (H / G);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int p = tok_pos[t];
   const int* r2t = req_to_token + req_idx[tok_b[t]] * ld_r2t;
@@ -239,11 +244,13 @@ extern "C" int b200_qk_norm_rope_write(const void* q, int64_t ldq, const void* k
                                        int q_group, int k_group, float eps, const float* freq_hi,
                                        const float* freq_lo, int rot_dims, const int* tok_pos,
                                        const int64_t* loc, void* pool, int64_t ld_pool, int k_off,
-                                       int v_off, float* q_out, int64_t ldqo, int T, int H, int G,
-                                       int D, int E, int dtype, void* stream) {
+                                       int v_off, float* q_out, int64_t ldqo, void* q_out16,
+                                       int64_t ldqo16, int T, int H, int G, int D, int E, int dtype,
+                                       void* stream) {
   using namespace b200;
   if (T == 0) return 0;
-  B200_REQUIRE(q && k && v && tok_pos && loc && pool && q_out, "b200_qk_norm_rope_write: null pointer");
+  B200_REQUIRE(q && k && v && tok_pos && loc && pool && (q_out || q_out16),
+               "b200_qk_norm_rope_write: null pointer");
   B200_REQUIRE(T > 0 && H > 0 && G > 0 && D > 0 && E > 0 && rot_dims >= 0 && rot_dims <= D &&
                    rot_dims % 2 == 0 && (rot_dims == 0 || freq_hi),
                "b200_qk_norm_rope_write: head size %d, rotated %d", D, rot_dims);
@@ -261,7 +268,7 @@ extern "C" int b200_qk_norm_rope_write(const void* q, int64_t ldq, const void* k
                 static_cast<const TT*>(q), ldq, static_cast<const TT*>(k), ldk,                      \
                 static_cast<const TT*>(v), ldv, qw, kw, q_group, k_group, eps, freq_hi, freq_lo,     \
                 rot_dims, tok_pos, loc, static_cast<TT*>(pool), ld_pool, k_off, v_off, q_out, ldqo,  \
-                H, G, D, E)
+                static_cast<TT*>(q_out16), ldqo16, H, G, D, E)
   if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
   else if (dtype == B200_F16) LAUNCH(__half);
   else if (dtype == B200_F32) LAUNCH(float);
@@ -275,7 +282,8 @@ extern "C" int b200_sink_attn(const float* q, int64_t ldq, const void* pool, int
                               int v_off, const int* req_to_token, int64_t ld_r2t,
                               const int64_t* req_idx, const int* tok_pos, const int* tok_b,
                               const float* sink, float scale, int window, int keep_first, void* out,
-                              int64_t ldo, int T, int H, int G, int D, int E, int dtype, void* stream) {
+                              int64_t ldo, int T, int H, int G, int D, int E, const int* tok_list,
+                              int dtype, void* stream) {
   using namespace b200;
   if (T == 0) return 0;
   B200_REQUIRE(q && pool && req_to_token && req_idx && tok_pos && tok_b && out,
@@ -293,7 +301,7 @@ extern "C" int b200_sink_attn(const float* q, int64_t ldq, const void* pool, int
   launch_kernel(sink_attn_kernel<TT, TT>, grid, dim3(kSinkWarps * 32), smem, st, 1, 0, q, ldq,       \
                 static_cast<const TT*>(pool), ld_pool, k_off, v_off, req_to_token, ld_r2t, req_idx,  \
                 tok_pos, tok_b, sink, scale, window, keep_first, static_cast<TT*>(out), ldo, H, G, D, \
-                E)
+                E, tok_list)
   if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
   else if (dtype == B200_F16) LAUNCH(__half);
   else if (dtype == B200_F32) LAUNCH(float);

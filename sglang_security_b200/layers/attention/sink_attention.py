@@ -8,7 +8,12 @@ row holds [keys | values] of all key/value heads (mem_cache/latent_pool.py's one
   * a learned sink per query head in the softmax denominator;
   * key size and value size that differ.
 Per step: one fused GEMM [q ; k ; v] (with bias), one launch that norms, rotates and writes the pool
-row, one attention launch over req_to_token (prompt portions and decoded tokens alike), W_o."""
+row, the attention over req_to_token, W_o.  The attention of a step is divided by batch entry: prompt
+portions of at least `tensor_core_min_tokens` tokens run on the tcgen05 extend kernel
+(csrc/attn_extend.cu: 16-bit operands, fp32 scores, maxima and sums; key and value size equal, 64 or
+128), decoded tokens and short portions on the CUDA-core kernel, which keeps the weights in fp32 too and
+is the only path of a 32-bit engine.  Both read the pool only, so a position's result does not depend
+on the cut of the prompt or on the batch beyond rounding."""
 from __future__ import annotations
 
 from typing import Optional
@@ -21,6 +26,9 @@ from ..linear import ColumnParallelLinear, RowParallelLinear
 
 
 class SinkAttention(nn.Module):
+    # prompt portions at least this long go to the tensor-core kernel (0 = never); tests lower it
+    tensor_core_min_tokens = 128
+
     def __init__(self, width: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float,
                  layer_id: int, eps: float, window: Optional[int] = None, keep_first: int = 0,
                  rope_base: float = 10000.0, rope_dims: int = 0, qk_norm: str = "whole",
@@ -64,6 +72,37 @@ class SinkAttention(nn.Module):
         dst = self.qkv_proj.bias if is_bias else self.qkv_proj.weight
         dst.data[lo:lo + self.sizes[i]].copy_(w)
 
+    def _tensor_core_ok(self, h: torch.Tensor) -> bool:
+        return (h.dtype in (torch.bfloat16, torch.float16) and self.dim == self.vdim and self.dim in (64, 128)
+                and self.tensor_core_min_tokens > 0)
+
+    @staticmethod
+    def _plan(fb, min_tokens: int):
+        """Which batch entries take the tensor-core kernel: their sub-tables (one host-to-device copy),
+        and the rows of all other tokens.  Shared by the layers of a step."""
+        key = ("sink_attn_plan", min_tokens)
+        if key in fb.extra:
+            return fb.extra[key]
+        ext, pre = fb.extend_seq_lens_cpu, fb.extend_prefix_lens_cpu
+        long = [b for b, n in enumerate(ext) if n >= min_tokens]
+        plan = None
+        if long:
+            starts, at = [], 0
+            for n in ext:
+                starts.append(at)
+                at += n
+            rest = [t for b, n in enumerate(ext) if n < min_tokens for t in range(starts[b], starts[b] + n)]
+            host = torch.tensor([long, [pre[b] for b in long], [ext[b] for b in long],
+                                 [starts[b] for b in long], [pre[b] + ext[b] for b in long]], dtype=torch.int64)
+            dev = host.to(fb.req_pool_indices.device, non_blocking=True)
+            plan = {"bs": len(long), "max_ext": max(ext[b] for b in long),
+                    "req": fb.req_pool_indices[dev[0]], "prefix": dev[1].to(torch.int32),
+                    "ext": dev[2].to(torch.int32), "start": dev[3].to(torch.int32), "seq": dev[4].contiguous(),
+                    "rest": (torch.tensor(rest, dtype=torch.int32).to(fb.req_pool_indices.device, non_blocking=True)
+                             if rest else None), "n_rest": len(rest)}
+        fb.extra[key] = plan
+        return plan
+
     def forward(self, h: torch.Tensor, fb) -> torch.Tensor:
         if not h.is_cuda:
             raise _lib.B200Error("SinkAttention: tensors must live on a CUDA device (no CPU path)")
@@ -76,22 +115,34 @@ class SinkAttention(nn.Module):
         if pool.dtype != h.dtype or pool.shape[1] != self.row_width:
             raise _lib.B200Error("SinkAttention: the token pool does not fit this layer")
         lib, st, code = _lib.load(), _lib.current_stream(), _lib.dtype_code(h.dtype)
-        q32 = torch.empty((T, H * D), dtype=torch.float32, device=h.device)
+        plan = self._plan(fb, self.tensor_core_min_tokens) if self._tensor_core_ok(h) else None
+        n_core = T if plan is None else plan["n_rest"]           # tokens of the CUDA-core kernel
+        q32 = torch.empty((T, H * D), dtype=torch.float32, device=h.device) if n_core else None
+        q16 = torch.empty((T, H * D), dtype=h.dtype, device=h.device) if plan is not None else None
         rot = self.rope_dims > 0
         rc = lib.b200_qk_norm_rope_write(
             q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
             _lib.ptr(self.q_norm_weight), _lib.ptr(self.k_norm_weight), self.q_group, self.k_group,
             self.eps, self.freq_hi.data_ptr() if rot else None, self.freq_lo.data_ptr() if rot else None,
             self.rope_dims, fb.tok_pos.data_ptr(), fb.out_cache_loc.data_ptr(), pool.data_ptr(),
-            pool.stride(0), 0, G * D, q32.data_ptr(), q32.stride(0), T, H, G, D, E, code, st)
+            pool.stride(0), 0, G * D, _lib.ptr(q32), H * D, _lib.ptr(q16), H * D, T, H, G, D, E, code, st)
         _lib.check(rc, "b200_qk_norm_rope_write")
         r2t = fb.req_to_token_pool.req_to_token
         out = torch.empty((T, H * E), dtype=h.dtype, device=h.device)
-        rc = lib.b200_sink_attn(
-            q32.data_ptr(), q32.stride(0), pool.data_ptr(), pool.stride(0), 0, G * D, r2t.data_ptr(),
-            r2t.stride(0), fb.req_pool_indices.data_ptr(), fb.tok_pos.data_ptr(), fb.tok_b.data_ptr(),
-            _lib.ptr(self.sink), self.scale, self.window, self.keep_first, out.data_ptr(), out.stride(0),
-            T, H, G, D, E, code, st)
-        _lib.check(rc, "b200_sink_attn")
+        if plan is not None:
+            rc = lib.b200_attn_extend_sink(
+                q16.data_ptr(), q16.stride(0), pool.data_ptr(), pool[:, G * D:].data_ptr(), pool.stride(0),
+                out.data_ptr(), out.stride(0), r2t.data_ptr(), r2t.stride(0), plan["req"].data_ptr(),
+                plan["seq"].data_ptr(), plan["prefix"].data_ptr(), plan["ext"].data_ptr(),
+                plan["start"].data_ptr(), plan["bs"], plan["max_ext"], H, G, D, E, self.scale, 0.0, 1.0, 1,
+                self.window, self.keep_first, _lib.ptr(self.sink), code, st)
+            _lib.check(rc, "b200_attn_extend_sink")
+        if n_core:
+            rc = lib.b200_sink_attn(
+                q32.data_ptr(), q32.stride(0), pool.data_ptr(), pool.stride(0), 0, G * D, r2t.data_ptr(),
+                r2t.stride(0), fb.req_pool_indices.data_ptr(), fb.tok_pos.data_ptr(), fb.tok_b.data_ptr(),
+                _lib.ptr(self.sink), self.scale, self.window, self.keep_first, out.data_ptr(), out.stride(0),
+                n_core, H, G, D, E, _lib.ptr(plan["rest"]) if plan is not None else None, code, st)
+            _lib.check(rc, "b200_sink_attn")
         res, _ = self.o_proj(out)
         return res

@@ -145,8 +145,9 @@ def test_recurrence_state_of_a_reused_slot_is_ignored():
 
 
 # ---- attention with window, kept first tokens and sink -----------------------------------------------
-def _attend(q, k, v, sink, scale, window, keep_first, cuts, dtype, page=16, seed=0):
-    """One sequence through qk_norm_rope_write (norm and rotation off) + sink_attn in portions `cuts`."""
+def _attend(q, k, v, sink, scale, window, keep_first, cuts, dtype, page=16, seed=0, tensor_core=False):
+    """One sequence through qk_norm_rope_write (norm and rotation off) + sink_attn in portions `cuts`;
+    tensor_core: the portions run on the tcgen05 extend kernel instead of the CUDA-core one."""
     from sglang_security_b200 import _lib
 
     T, H, D = q.shape
@@ -160,17 +161,32 @@ def _attend(q, k, v, sink, scale, window, keep_first, cuts, dtype, page=16, seed
         fb = hb.step([(0, n)])
         qq, kk, vv = (t[at:at + n].reshape(n, -1).to(dtype).to(DEV).contiguous() for t in (q, k, v))
         q32 = torch.empty((n, H * D), dtype=torch.float32, device=DEV)
+        q16 = torch.empty((n, H * D), dtype=dtype, device=DEV)
         rc = lib.b200_qk_norm_rope_write(qq.data_ptr(), qq.stride(0), kk.data_ptr(), kk.stride(0), vv.data_ptr(),
                                          vv.stride(0), None, None, 0, 0, 1e-6, None, None, 0, fb.tok_pos.data_ptr(),
                                          fb.out_cache_loc.data_ptr(), pool.data_ptr(), pool.stride(0), 0, G * D,
-                                         q32.data_ptr(), q32.stride(0), n, H, G, D, E, code, 0)
+                                         q32.data_ptr(), q32.stride(0), q16.data_ptr(), q16.stride(0), n, H, G, D, E,
+                                         code, 0)
         _lib.check(rc, "prep")
         out = torch.empty((n, H * E), dtype=dtype, device=DEV)
         sink_d = sink.float().to(DEV) if sink is not None else None
+        if tensor_core:
+            i32 = lambda x: torch.tensor([x], dtype=torch.int32, device=DEV)
+            seq, pre, ext, start = torch.tensor([at + n], device=DEV), i32(at), i32(n), i32(0)
+            rc = lib.b200_attn_extend_sink(
+                q16.data_ptr(), q16.stride(0), pool.data_ptr(), pool[:, G * D:].data_ptr(), pool.stride(0),
+                out.data_ptr(), out.stride(0), fb.req_to_token.data_ptr(), fb.req_to_token.stride(0),
+                fb.req_pool_indices.data_ptr(), seq.data_ptr(), pre.data_ptr(), ext.data_ptr(), start.data_ptr(), 1, n,
+                H, G, D, E, scale, 0.0, 1.0, 1, window or 0, keep_first, _lib.ptr(sink_d), code, 0)
+            _lib.check(rc, "extend")
+            torch.cuda.synchronize()
+            outs.append(out.cpu())
+            at += n
+            continue
         rc = lib.b200_sink_attn(q32.data_ptr(), q32.stride(0), pool.data_ptr(), pool.stride(0), 0, G * D,
                                 fb.req_to_token.data_ptr(), fb.req_to_token.stride(0), fb.req_pool_indices.data_ptr(),
                                 fb.tok_pos.data_ptr(), fb.tok_b.data_ptr(), _lib.ptr(sink_d),
-                                scale, window or 0, keep_first, out.data_ptr(), out.stride(0), n, H, G, D, E, code, 0)
+                                scale, window or 0, keep_first, out.data_ptr(), out.stride(0), n, H, G, D, E, None, code, 0)
         _lib.check(rc, "attn")
         torch.cuda.synchronize()
         outs.append(out.cpu())
@@ -225,6 +241,37 @@ def test_window_edges_kept_tokens_and_far_keys_stand_out(decode):
     assert got.abs().max() > 50
 
 
+@pytest.mark.parametrize("H,G,D,window,keep", [(4, 2, 64, 40, 4), (8, 1, 128, 200, 70), (2, 2, 64, 7, 0),
+                                               (6, 2, 128, None, 0), (3, 3, 64, 130, 129), (16, 2, 64, 65, 1)])
+def test_sink_attention_on_the_tensor_core_kernel(H, G, D, window, keep):
+    T = 450
+    q, k, v = _qkv(T, H, G, D, D, 61, torch.bfloat16)
+    sink = torch.randn(H, generator=torch.Generator().manual_seed(62)) + 1.0
+    want = P.sink_softmax(q, k, v, D ** -0.5, window, keep, sink.double())
+    for cuts in ([T], [200, 130, 1, 119], [63, 64, 65, 258]):
+        got = _attend(q, k, v, sink, D ** -0.5, window, keep, cuts, torch.bfloat16, tensor_core=True)
+        assert _err(got, want) <= TOL[torch.bfloat16], cuts
+
+
+def test_tensor_core_kernel_sees_the_edges():
+    """As above with one outstanding key: just inside / outside the window, among / after the kept
+    tokens, at tile borders (64 keys), far back."""
+    T, H, G, D, window, keep = 400, 2, 1, 64, 100, 3
+    base_q, base_k, base_v = _qkv(T, H, G, D, D, 63, torch.bfloat16)
+    query = T - 1
+    cases = {query - window + 1: True, query - window: False, keep - 1: True, keep: False, 0: True, 63: False,
+             64: False, 320: True, 319: True, query: True}
+    for key, seen in cases.items():
+        q, k, v = base_q.clone(), base_k.clone() * 0.1, base_v.clone()
+        k[key, 0] = (q[query, 0] / q[query, 0].norm() * 40.0).bfloat16().double()
+        v[key, 0] = 100.0
+        for cuts in ([T], [T - 70, 70]):
+            got = _attend(q, k, v, torch.zeros(H), 1.0, window, keep, cuts, torch.bfloat16, tensor_core=True)[query, 0]
+            assert (got.abs().max() > 50) == seen, (key, seen, cuts)
+        want = P.sink_softmax(q, k, v, 1.0, window, keep, torch.zeros(H, dtype=P.DT))[query, 0]
+        assert _err(got, want) <= 2e-2
+
+
 def test_sink_changes_the_denominator_only():
     T, H, G, D, E = 20, 2, 2, 8, 8
     q, k, v = _qkv(T, H, G, D, E, 31, torch.float32)
@@ -259,8 +306,8 @@ def test_qk_norm_and_partial_rotation(group):
     rc = _lib.load().b200_qk_norm_rope_write(
         qd.data_ptr(), qd.stride(0), kd.data_ptr(), kd.stride(0), vd.data_ptr(), vd.stride(0), qwd.data_ptr(),
         kwd.data_ptr(), qg, kg, eps, hid.data_ptr(), lod.data_ptr(), dims, posd.data_ptr(),
-        locd.data_ptr(), pool.data_ptr(), pool.stride(0), 0, G * D, q32.data_ptr(), q32.stride(0), n, H, G, D, E,
-        _lib.F32, 0)
+        locd.data_ptr(), pool.data_ptr(), pool.stride(0), 0, G * D, q32.data_ptr(), q32.stride(0), None, 0, n, H, G,
+        D, E, _lib.F32, 0)
     _lib.check(rc, "prep")
 
     def want(x, w, heads):

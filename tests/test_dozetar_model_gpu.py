@@ -28,6 +28,12 @@ CONFIGS = {
                            (U.parallel(heads=1, kv_heads=1, dim=8, vdim=8, window=2, keep_first=5, rot_dims=4,
                                        r_heads=1, r_dim=4, r_vdim=4), None),
                            (U.mlstm(heads=1, dim=4, vdim=4, cap=3.0), None)], vocab=33, width=24, mult=0.3),
+    # attention sizes the tensor-core kernel takes (key size = value size = 64), grouped 4 : 1
+    "d": lambda: U.config([(U.parallel(heads=4, kv_heads=1, dim=64, vdim=64, window=50, keep_first=3, rot_dims=32,
+                                       r_heads=2, r_dim=16, r_vdim=16), U.experts(4, 2, 32)),
+                           (U.mlstm(heads=2, dim=16, vdim=16), None),
+                           (U.parallel(heads=2, kv_heads=2, dim=64, vdim=64, window=None, rot_dims=64, r_heads=1,
+                                       r_dim=8, r_vdim=8), None)], vocab=101, width=64),
 }
 
 
@@ -146,6 +152,33 @@ def test_batch_does_not_change_a_request_fp32(tmp_path):
     both.step([("b", b[:30]), ("a", a[:50])])
     both.step([("a", a[50:]), ("b", b[30:31])])
     assert (alone.result("a") - both.result("a")).abs().max() <= 1e-4
+
+
+@pytest.mark.parametrize("sharp", [False, True])
+def test_long_portions_on_the_tensor_core_kernel_beside_decoded_tokens(tmp_path, monkeypatch, sharp):
+    """Portions of 16 tokens and more take the tcgen05 kernel, shorter ones and decoded tokens the
+    CUDA-core kernel, in the same step; every cut must give the whole prompt's logits."""
+    from sglang_security_b200.layers.attention.sink_attention import SinkAttention
+
+    monkeypatch.setattr(SinkAttention, "tensor_core_min_tokens", 16)
+    cfg, w, folder = _model(tmp_path, "d", sharp=sharp)
+    a, b = _tokens(cfg, 300, 40), _tokens(cfg, 170, 41)
+    want_a, want_b = P.forward(cfg, w, a), P.forward(cfg, w, b)
+    tol = (TOL_SHARP if sharp else TOL)[torch.bfloat16]
+    d = U.Driver(folder, torch.bfloat16)
+    d.step([("a", a)], end=["a"])
+    assert U.rel_err(d.result("a"), want_a, torch.bfloat16) <= tol
+    d = U.Driver(folder, torch.bfloat16)
+    d.step([("a", a[:130]), ("b", b[:5])])
+    d.step([("a", a[130:131]), ("b", b[5:150])])
+    d.step([("a", a[131:290]), ("b", b[150:151])])
+    d.step([("a", a[290:]), ("b", b[151:])])
+    assert U.rel_err(d.result("a"), want_a, torch.bfloat16) <= tol
+    assert U.rel_err(d.result("b"), want_b, torch.bfloat16) <= tol
+    monkeypatch.setattr(SinkAttention, "tensor_core_min_tokens", 0)        # the CUDA-core kernel alone agrees
+    d = U.Driver(folder, torch.bfloat16)
+    d.step([("a", a)], end=["a"])
+    assert U.rel_err(d.result("a"), want_a, torch.bfloat16) <= tol
 
 
 def test_long_decoding(tmp_path):
