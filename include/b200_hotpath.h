@@ -625,25 +625,28 @@ int b200_softcap_rows(const void* z, int64_t ldz, float* out, int64_t ldo, int T
                       int dtype, void* stream);
 
 /* Matrix-state linear recurrence per (batch entry, head) over the entry's new tokens, state fp32:
- *   S_t = a_t S_(t-1) + b_t k_t v_t^T ;  o_t = S_t^T (q_scale q_t)   [/ den_t]
+ *   S_t = a_t S_(t-1) + b_t k_t v_t^T ;  o_t = S_t^T (q_scale q_t)
  * decay given (fp32 [H]): a_t = decay[h], b_t = 1.  gates given (fp32 [T, 2H], input then forget
  * pre-activations): li = cap tanh(zi / cap), lf = logsigmoid(cap tanh(zf / cap)) (cap <= 0: uncapped),
- * m_t = max(lf + m_(t-1), li) with m_0 = 0, a_t = exp(lf + m_(t-1) - m_t), b_t = exp(li - m_t),
- * n_t = a_t n_(t-1) + b_t k_t, den_t = max(|n_t . q_t|, exp(-m_t)) + den_eps.  act 1 applies silu to
- * q, k and v first.  q, k [T, H * D], v [T, H * E] (row strides given), out fp32 [T, H * E].  The
- * state row state[slot[b]] (b200_linear_recurrence_state_width floats) is read unless the entry's
- * first token is at position 0 and written at the end.                                             */
+ * m_t = max(lf + m_(t-1), li) with m_0 = 0, a_t = exp(lf + m_(t-1) - m_t), b_t = exp(li - m_t), and the
+ * normaliser n_t = a_t n_(t-1) + b_t k_t; then aux (fp32 [T, 2H]) receives n_t . q_t and m_t and the
+ * consumer divides o_t by max(|n_t . q_t|, exp(-m_t)) + den_eps (b200_gated_group_rmsnorm does).
+ * act 1 applies silu to q, k and v first.  q, k [T, H * D], v [T, H * E] (row strides given), out fp32
+ * [T, H * E].  The state row state[slot[b]] (b200_linear_recurrence_state_width floats, layout private
+ * to the kernel) is read unless the entry's first token is at position 0 and written at the end.    */
 int64_t b200_linear_recurrence_state_width(int H, int D, int E, int gated);
 int b200_linear_recurrence(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
                            int64_t ldv, const float* gates, int64_t ldg, const float* decay, float cap,
-                           float q_scale, float den_eps, int act, float* state, int64_t ld_state,
-                           const int64_t* slot, const int* tok_pos, const int* ext_start,
-                           const int* ext_len, float* out, int64_t ldo, int batch, int H, int D, int E,
+                           float q_scale, int act, float* state, int64_t ld_state, const int64_t* slot,
+                           const int* tok_pos, const int* ext_start, const int* ext_len, float* out,
+                           int64_t ldo, float* aux, int64_t ld_aux, int batch, int H, int D, int E,
                            int dtype, void* stream);
 /* out = o / sqrt(mean over each group of `group` coordinates (o^2) + eps) * w * sigmoid(z); w and z
- * optional; o fp32, z and out in the model dtype.                                                  */
+ * optional; o fp32, z and out in the model dtype.  With aux (fp32 [T, 2H] from the gated recurrence)
+ * head hd of o is first divided by max(|aux[t, hd]|, exp(-aux[t, H + hd])) + den_eps.               */
 int b200_gated_group_rmsnorm(const float* o, int64_t ldo, const float* w, const void* z, int64_t ldz,
-                             void* out, int64_t ldout, int T, int N, int group, float eps, int dtype,
+                             void* out, int64_t ldout, int T, int N, int group, float eps,
+                             const float* aux, int64_t ld_aux, int H, float den_eps, int dtype,
                              void* stream);
 
 /* Attention with a sink, step 1: q (H heads) and k (G heads) of size D are RMS-normed in groups of

@@ -198,11 +198,12 @@ _SIGNATURES = {
                                   c_void_p]),
     "b200_linear_recurrence_state_width": (c_int64, [c_int, c_int, c_int, c_int]),
     "b200_linear_recurrence": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
-                                       c_int64, c_void_p, c_float, c_float, c_float, c_int, c_void_p,
-                                       c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
-                                       c_int, c_int, c_int, c_int, c_int, c_void_p]),
+                                       c_int64, c_void_p, c_float, c_float, c_int, c_void_p, c_int64,
+                                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+                                       c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_gated_group_rmsnorm": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
-                                         c_int, c_int, c_int, c_float, c_int, c_void_p]),
+                                         c_int, c_int, c_int, c_float, c_void_p, c_int64, c_int, c_float,
+                                         c_int, c_void_p]),
     "b200_qk_norm_rope_write": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
                                         c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_int,
                                         c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,

@@ -1,32 +1,47 @@
 // Matrix-state linear recurrences over a mixed batch, state in fp32 and carried per sequence:
 //
-//   S_t = a_t S_(t-1) + b_t k_t v_t^T        S [D, E] per head        o_t = S_t^T q_t  (/ den_t)
+//   S_t = a_t S_(t-1) + b_t k_t v_t^T        S [D, E] per head        o_t = S_t^T q_t
 //
-//   kDecay : a_t = decay[head] (constant), b_t = 1, no denominator        (decayed linear attention)
-//   kExpGates : log-space input and forget gates with a running stabiliser m (m_0 = 0):
+//   decay form : a_t = decay[head] (constant), b_t = 1                     (decayed linear attention)
+//   gated form : log-space input and forget gates with a running stabiliser m (m_0 = 0):
 //             li = cap tanh(zi / cap), lf = logsigmoid(cap tanh(zf / cap))   (cap <= 0: no capping)
 //             m_t = max(lf + m_(t-1), li), a_t = exp(lf + m_(t-1) - m_t), b_t = exp(li - m_t)
-//             n_t = a_t n_(t-1) + b_t k_t ;  den_t = max(|n_t . q_t|, exp(-m_t)) + den_eps     (mLSTM)
+//             and the normaliser n_t = a_t n_(t-1) + b_t k_t, which is the same recurrence for one more
+//             value column that is always 1.  The kernel returns the un-normalised o_t together with
+//             n_t . q_t and m_t per (token, head); the consumer divides by
+//             max(|n_t . q_t|, exp(-m_t)) + den_eps                                          (mLSTM)
 //
-// One CTA owns (batch entry, head, a slice of the E columns) and walks the entry's new tokens in
-// order, so a token's result is the same sum in the same order however the sequence was cut into
-// steps.  A thread keeps S[d][e] for one column e and the rows d = p, p + P, ... in registers (P
-// lanes of a warp share a column and add their partial dot products by shuffles).  The state row of a
-// sequence is read when its portion does not start at position 0 (there it is zero) and written back
-// at the end; a single decoded token is the same kernel with a portion of one.
+// One CTA of 64 threads owns (batch entry, head, a slice of the value columns) and walks the entry's
+// new tokens in order, so a token's result is the same sum in the same order however the sequence
+// was cut into steps.  A thread keeps 16 consecutive rows d of TWO neighbouring columns in registers
+// as float2 (packed two-wide fp32 multiply-adds); the P lanes that share a column pair add their
+// partial dot products by shuffles.  Tokens are staged a chunk (up to 32) at a time: the raw q, k, v rows
+// of the NEXT chunk stream into shared memory with cp.async while the current chunk is computed, then
+// one pass converts them to fp32 (activation, query scale, zero padding to P * 16 rows); rows that are
+// not 8-byte aligned are staged with plain loads instead.  The gated form's scalar chain m_t runs once
+// per chunk in one lane, the exponentials beside it in parallel.  The state row of a sequence is read when its
+// portion does not start at position 0 (there it is zero) and written back at the end; a single
+// decoded token is the same kernel with a portion of one.  The state's layout is the kernel's own
+// (per head and slice: [row][thread] float2, then m), so every access is coalesced;
+// b200_linear_recurrence_state_width gives its size.
 //
 //   gated_group_rmsnorm : out = o / sqrt(mean_group(o^2) + eps) * w * sigmoid(z), the mean taken over
-//                         consecutive groups of `group` coordinates (one head, or the whole row).
+//                         consecutive groups of `group` coordinates (one head, or the whole row);
+//                         with the gated form's (n . q, m) per head, o is first divided as above.
 #include "common.cuh"
 
 namespace b200 {
 
-constexpr int kRecThreads = 256;
-constexpr int kRecRows = 32;     // rows of S per thread: D <= 32 * P, P <= 32
-constexpr int kRecChunk = 16;    // tokens staged in shared memory at a time
+constexpr int kRecThreads = 64;
+constexpr int kRecRows = 16;     // rows of S per thread: D <= 16 * P, P <= 32
+constexpr int kRecChunk = 32;    // most tokens staged in shared memory at a time
+constexpr int kRecSlice = kRecRows * kRecThreads * 2 + 2;   // floats of one slice's state (+ m, pad)
 
 __device__ __forceinline__ float rec_act(float z, int act) {
   return act == 1 ? z / (1.0f + expf(-z)) : z;
+}
+__device__ __forceinline__ void cp_async8(uint32_t smem_addr, const void* gptr) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(smem_addr), "l"(gptr));
 }
 __device__ __forceinline__ float log_sigmoid(float z) {
   return fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
@@ -37,119 +52,200 @@ __global__ void __launch_bounds__(kRecThreads)
 linear_recurrence_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k, int64_t ldk,
                          const T* __restrict__ v, int64_t ldv, const float* __restrict__ gates,
                          int64_t ldg, const float* __restrict__ decay, float cap, float q_scale,
-                         float den_eps, int act, float* __restrict__ state, int64_t ld_state,
+                         int act, float* __restrict__ state, int64_t ld_state,
                          const int64_t* __restrict__ slot, const int* __restrict__ tok_pos,
                          const int* __restrict__ ext_start, const int* __restrict__ ext_len,
-                         float* __restrict__ out, int64_t ldo, int H, int D, int E, int P) {
-  extern __shared__ float rec_smem[];
-  const int ES = kRecThreads / P;
-  float* qs = rec_smem;                       // [chunk][D]
-  float* ks = qs + kRecChunk * D;             // [chunk][D]
-  float* vs = ks + kRecChunk * D;             // [chunk][ES]
-  float* gi = vs + kRecChunk * ES;            // [chunk]
-  float* gf = gi + kRecChunk;                 // [chunk]
+                         float* __restrict__ out, int64_t ldo, float* __restrict__ aux, int64_t ld_aux,
+                         int H, int D, int E, int P, int CH, int stream_rows) {
+  extern __shared__ __align__(16) float rec_smem[];
+  const int Dp = P * kRecRows;                // padded key size
+  const int ES = 2 * (kRecThreads / P);       // value columns of this CTA
+  float* qs = rec_smem;                       // [CH][Dp]
+  float* ks = qs + CH * Dp;                   // [CH][Dp]
+  float* vs = ks + CH * Dp;                   // [CH][ES]
+  float* ga = vs + CH * ES;                   // [32] a_t
+  float* gb = ga + kRecChunk;                 // [32] b_t
+  float* gm = gb + kRecChunk;                 // [32] m_t
+  float* gl = gm + kRecChunk;                 // [2][32] li, lf
+  // raw rows in flight, two stages of [CH][2 D + ES] values of T (8-byte pieces)
+  T* raw = reinterpret_cast<T*>(gl + 2 * kRecChunk);
+  const int raw_stage = CH * (2 * D + ES);
   const int b = blockIdx.z, h = blockIdx.y, e0 = blockIdx.x * ES;
-  const int tid = threadIdx.x, p = tid % P, col = tid / P, e = e0 + col;
+  const int tid = threadIdx.x, p = tid % P, cp = tid / P, e = e0 + 2 * cp;
   const int start = ext_start[b], len = ext_len[b];
   if (len <= 0) return;
   const bool fresh = tok_pos[start] == 0;
-  // per head: S [D][E], then (gated form) one copy of (n [D], m) per column slice, so that no CTA
-  // reads what another CTA of the same launch writes
-  const int64_t head_state = static_cast<int64_t>(D) * E + (GATES ? gridDim.x * (D + 1) : 0);
-  float* st = state + slot[b] * ld_state + h * head_state;
-  float* sn = st + static_cast<int64_t>(D) * E + blockIdx.x * (D + 1);
-  float s[kRecRows], nr[GATES ? kRecRows : 1];
-  float m = 0.f;
+  float* st = state + slot[b] * ld_state + (static_cast<int64_t>(h) * gridDim.x + blockIdx.x) * kRecSlice;
+  float2* st2 = reinterpret_cast<float2*>(st);
+  float2 s[kRecRows];
 #pragma unroll
-  for (int r = 0; r < kRecRows; ++r) {
-    const int d = p + r * P;
-    s[r] = (!fresh && d < D && e < E) ? st[static_cast<int64_t>(d) * E + e] : 0.f;
-    if (GATES) nr[r] = (!fresh && d < D) ? sn[d] : 0.f;
-  }
-  if (GATES && !fresh) m = sn[D];
+  for (int r = 0; r < kRecRows; ++r) s[r] = fresh ? make_float2(0.f, 0.f) : st2[r * kRecThreads + tid];
+  float m = (GATES && !fresh) ? st[kRecSlice - 2] : 0.f;
   const float lam = GATES ? 0.f : decay[h];
-  for (int c0 = 0; c0 < len; c0 += kRecChunk) {
-    const int n = min(kRecChunk, len - c0);
-    __syncthreads();
-    for (int idx = tid; idx < n * D; idx += kRecThreads) {
-      const int j = idx / D, d = idx - j * D;
+  const int ncols = E + (GATES ? 1 : 0);      // the gated form's last column is the normaliser (v = 1)
+  const int vvalid = max(0, min(ES, E - e0));  // value columns of this slice that exist
+  constexpr int PE = 8 / sizeof(T);            // values per 8-byte piece
+  auto issue_chunk = [&](int c0, int stage) {
+    const int n = min(CH, len - c0);
+    T* rq = raw + stage * raw_stage;
+    T* rk = rq + CH * D;
+    T* rv = rk + CH * D;
+    const int dp = D / PE, vp = vvalid / PE;
+    for (int idx = tid; idx < n * dp; idx += kRecThreads) {
+      const int j = idx / dp, c = idx - j * dp;
       const int64_t row = start + c0 + j;
-      qs[j * D + d] = rec_act(to_float<T>(q[row * ldq + h * D + d]), act) * q_scale;
-      ks[j * D + d] = rec_act(to_float<T>(k[row * ldk + h * D + d]), act);
+      cp_async8(smem_u32(rq + j * D + c * PE), q + row * ldq + h * D + c * PE);
+      cp_async8(smem_u32(rk + j * D + c * PE), k + row * ldk + h * D + c * PE);
+    }
+    for (int idx = tid; idx < n * vp; idx += kRecThreads) {
+      const int j = idx / vp, c = idx - j * vp;
+      const int64_t row = start + c0 + j;
+      cp_async8(smem_u32(rv + j * ES + c * PE), v + row * ldv + h * E + e0 + c * PE);
+    }
+    cp_async_commit();
+  };
+  float gi_next = 0.f, gf_next = 0.f;          // gate pre-activations of the next chunk (warp 0)
+  auto load_gates = [&](int c0) {
+    if (GATES && tid < 32 && c0 + tid < len) {
+      const int64_t row = start + c0 + tid;
+      gi_next = gates[row * ldg + h];
+      gf_next = gates[row * ldg + H + h];
+    }
+  };
+  if (stream_rows) issue_chunk(0, 0);
+  load_gates(0);
+  for (int c0 = 0; c0 < len; c0 += CH) {
+    const int n = min(CH, len - c0);
+    const int stage = (c0 / CH) & 1;
+    if (stream_rows) {
+      if (c0 + CH < len) {
+        issue_chunk(c0 + CH, stage ^ 1);
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+    }
+    __syncthreads();
+    const T* rq = raw + stage * raw_stage;
+    const T* rk = rq + CH * D;
+    const T* rv = rk + CH * D;
+    for (int idx = tid; idx < n * Dp; idx += kRecThreads) {
+      const int j = idx / Dp, d = idx - j * Dp;
+      const int64_t row = start + c0 + j;
+      float qv = 0.f, kv = 0.f;
+      if (d < D) {
+        qv = to_float<T>(stream_rows ? rq[j * D + d] : q[row * ldq + h * D + d]);
+        kv = to_float<T>(stream_rows ? rk[j * D + d] : k[row * ldk + h * D + d]);
+        qv = rec_act(qv, act) * q_scale;
+        kv = rec_act(kv, act);
+      }
+      qs[idx] = qv;
+      ks[idx] = kv;
     }
     for (int idx = tid; idx < n * ES; idx += kRecThreads) {
       const int j = idx / ES, c = idx - j * ES;
       const int64_t row = start + c0 + j;
-      vs[j * ES + c] = (e0 + c < E) ? rec_act(to_float<T>(v[row * ldv + h * E + e0 + c]), act) : 0.f;
+      float x = 0.f;
+      if (e0 + c < E)
+        x = rec_act(to_float<T>(stream_rows ? rv[j * ES + c] : v[row * ldv + h * E + e0 + c]), act);
+      else if (GATES && e0 + c == E) x = 1.f;
+      vs[idx] = x;
     }
-    if (GATES && tid < n) {
-      const int64_t row = start + c0 + tid;
-      float zi = gates[row * ldg + h], zf = gates[row * ldg + H + h];
-      if (cap > 0.f) {
-        zi = cap * tanhf(zi / cap);
-        zf = cap * tanhf(zf / cap);
+    if (GATES && tid < 32) {
+      // gate values of the chunk in parallel, the stabiliser chain in one lane, the exponentials
+      // in parallel again
+      float li = 0.f, lf = 0.f;
+      if (tid < n) {
+        li = gi_next;
+        lf = gf_next;
+        if (cap > 0.f) {
+          li = cap * tanhf(li / cap);
+          lf = cap * tanhf(lf / cap);
+        }
+        lf = log_sigmoid(lf);
+        gl[tid] = li;
+        gl[kRecChunk + tid] = lf;
       }
-      gi[tid] = zi;
-      gf[tid] = log_sigmoid(zf);
-    }
-    __syncthreads();
-    for (int j = 0; j < n; ++j) {
-      float a = lam, bb = 1.f;
-      if (GATES) {
-        const float li = gi[j], lf = gf[j];
-        const float mn = fmaxf(lf + m, li);
-        a = expf(lf + m - mn);
-        bb = expf(li - mn);
-        m = mn;
-      }
-      const float ve = vs[j * ES + col] * bb;
-      const float* kj = ks + j * D;
-      const float* qj = qs + j * D;
-      float acc = 0.f, accn = 0.f;
-#pragma unroll
-      for (int r = 0; r < kRecRows; ++r) {
-        const int d = p + r * P;
-        if (d < D) {
-          const float kd = kj[d], qd = qj[d];
-          s[r] = fmaf(a, s[r], kd * ve);
-          acc = fmaf(s[r], qd, acc);
-          if (GATES) {
-            nr[r] = fmaf(a, nr[r], bb * kd);
-            accn = fmaf(nr[r], qd, accn);
-          }
+      __syncwarp();
+      if (tid == 0) {
+        float mm = m;
+        for (int j = 0; j < n; ++j) {
+          mm = fmaxf(gl[kRecChunk + j] + mm, gl[j]);
+          gm[j] = mm;
         }
       }
-      for (int o = P >> 1; o > 0; o >>= 1) {
-        acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (GATES) accn += __shfl_xor_sync(0xffffffffu, accn, o);
+      __syncwarp();
+      if (tid < n) {
+        const float mp = tid == 0 ? m : gm[tid - 1];
+        ga[tid] = expf(lf + mp - gm[tid]);
+        gb[tid] = expf(li - gm[tid]);
       }
-      if (p == 0 && e < E) {
-        float y = acc;
-        if (GATES) y = acc / (fmaxf(fabsf(accn), expf(-m)) + den_eps);
-        out[(start + c0 + j) * ldo + h * E + e] = y;
+    }
+    __syncthreads();
+    load_gates(c0 + CH);                      // in flight during this chunk's tokens
+    if (GATES) {
+      m = gm[n - 1];
+      if (aux && blockIdx.x == 0 && tid < n) aux[(start + c0 + tid) * ld_aux + H + h] = gm[tid];
+    }
+#pragma unroll 2
+    for (int j = 0; j < n; ++j) {
+      const float a = GATES ? ga[j] : lam, bb = GATES ? gb[j] : 1.f;
+      const float2 a2 = make_float2(a, a);
+      const float2 vv = *reinterpret_cast<const float2*>(vs + j * ES + 2 * cp);
+      const float2 ve = make_float2(vv.x * bb, vv.y * bb);
+      const float4* k4 = reinterpret_cast<const float4*>(ks + j * Dp + p * kRecRows);
+      const float4* q4 = reinterpret_cast<const float4*>(qs + j * Dp + p * kRecRows);
+      float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int r4 = 0; r4 < kRecRows / 4; ++r4) {
+        const float4 kk = k4[r4], qq = q4[r4];
+        s[4 * r4] = ffma2(a2, s[4 * r4], fmul2(make_float2(kk.x, kk.x), ve));
+        acc0 = ffma2(s[4 * r4], make_float2(qq.x, qq.x), acc0);
+        s[4 * r4 + 1] = ffma2(a2, s[4 * r4 + 1], fmul2(make_float2(kk.y, kk.y), ve));
+        acc1 = ffma2(s[4 * r4 + 1], make_float2(qq.y, qq.y), acc1);
+        s[4 * r4 + 2] = ffma2(a2, s[4 * r4 + 2], fmul2(make_float2(kk.z, kk.z), ve));
+        acc0 = ffma2(s[4 * r4 + 2], make_float2(qq.z, qq.z), acc0);
+        s[4 * r4 + 3] = ffma2(a2, s[4 * r4 + 3], fmul2(make_float2(kk.w, kk.w), ve));
+        acc1 = ffma2(s[4 * r4 + 3], make_float2(qq.w, qq.w), acc1);
+      }
+      float ax = acc0.x + acc1.x, ay = acc0.y + acc1.y;
+      for (int o = P >> 1; o > 0; o >>= 1) {
+        ax += __shfl_xor_sync(0xffffffffu, ax, o);
+        ay += __shfl_xor_sync(0xffffffffu, ay, o);
+      }
+      if (p == 0) {
+        const int64_t row = start + c0 + j;
+        if (e < E) out[row * ldo + h * E + e] = ax;
+        else if (GATES && e == E && aux) aux[row * ld_aux + h] = ax;
+        if (e + 1 < E) out[row * ldo + h * E + e + 1] = ay;
+        else if (GATES && e + 1 == E && aux) aux[row * ld_aux + h] = ay;
       }
     }
   }
+  if (e < ncols) {
 #pragma unroll
-  for (int r = 0; r < kRecRows; ++r) {
-    const int d = p + r * P;
-    if (d < D && e < E) st[static_cast<int64_t>(d) * E + e] = s[r];
-    if (GATES && d < D && col == 0) sn[d] = nr[r];
+    for (int r = 0; r < kRecRows; ++r) st2[r * kRecThreads + tid] = s[r];
   }
-  if (GATES && tid == 0) sn[D] = m;
+  if (GATES && tid == 0) st[kRecSlice - 2] = m;
 }
 
 template <typename TZ, typename TO>
 __global__ void __launch_bounds__(256)
 gated_group_rmsnorm_kernel(const float* __restrict__ o, int64_t ldo, const float* __restrict__ w,
                            const TZ* __restrict__ z, int64_t ldz, TO* __restrict__ out, int64_t ldout,
-                           int N, int group, float eps) {
+                           int N, int group, float eps, const float* __restrict__ aux, int64_t ld_aux,
+                           int H, float den_eps) {
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float* row = o + t * ldo;
+  const int head_size = aux ? N / H : 1;
   for (int g0 = warp * group; g0 < N; g0 += 8 * group) {
     float ss = 0.f;
     for (int d = lane; d < group; d += 32) {
-      const float x = row[g0 + d];
+      float x = row[g0 + d];
+      if (aux) {
+        const int hd = (g0 + d) / head_size;
+        x /= fmaxf(fabsf(aux[t * ld_aux + hd]), expf(-aux[t * ld_aux + H + hd])) + den_eps;
+      }
       ss = fmaf(x, x, ss);
     }
 #pragma unroll
@@ -157,6 +253,10 @@ gated_group_rmsnorm_kernel(const float* __restrict__ o, int64_t ldo, const float
     const float r = 1.0f / sqrtf(ss / static_cast<float>(group) + eps);
     for (int d = lane; d < group; d += 32) {
       float y = row[g0 + d] * r;
+      if (aux) {
+        const int hd = (g0 + d) / head_size;
+        y /= fmaxf(fabsf(aux[t * ld_aux + hd]), expf(-aux[t * ld_aux + H + hd])) + den_eps;
+      }
       if (w) y *= w[g0 + d];
       if (z) y *= 1.0f / (1.0f + expf(-to_float<TZ>(z[t * ldz + g0 + d])));
       out[t * ldout + g0 + d] = from_float<TO>(y);
@@ -172,36 +272,52 @@ static int rec_parts(int D) {
   return P;
 }
 
-// fp32 values one sequence keeps per layer (see the layout in the kernel)
+// fp32 values one sequence keeps per layer (the layout is the kernel's own)
 extern "C" int64_t b200_linear_recurrence_state_width(int H, int D, int E, int gated) {
   if (H <= 0 || D <= 0 || E <= 0 || D > b200::kRecRows * 32) return -1;
-  const int slices = b200::ceil_div(E, b200::kRecThreads / rec_parts(D));
-  return static_cast<int64_t>(H) * (static_cast<int64_t>(D) * E + (gated ? slices * (D + 1) : 0));
+  const int es = 2 * (b200::kRecThreads / rec_parts(D));
+  const int slices = b200::ceil_div(E + (gated ? 1 : 0), es);
+  return static_cast<int64_t>(H) * slices * b200::kRecSlice;
 }
 
 extern "C" int b200_linear_recurrence(const void* q, int64_t ldq, const void* k, int64_t ldk,
                                       const void* v, int64_t ldv, const float* gates, int64_t ldg,
-                                      const float* decay, float cap, float q_scale, float den_eps,
-                                      int act, float* state, int64_t ld_state, const int64_t* slot,
+                                      const float* decay, float cap, float q_scale, int act,
+                                      float* state, int64_t ld_state, const int64_t* slot,
                                       const int* tok_pos, const int* ext_start, const int* ext_len,
-                                      float* out, int64_t ldo, int batch, int H, int D, int E,
-                                      int dtype, void* stream) {
+                                      float* out, int64_t ldo, float* aux, int64_t ld_aux, int batch,
+                                      int H, int D, int E, int dtype, void* stream) {
   using namespace b200;
   if (batch == 0) return 0;
   B200_REQUIRE(q && k && v && state && slot && tok_pos && ext_start && ext_len && out,
                "b200_linear_recurrence: null pointer");
   B200_REQUIRE((gates != nullptr) != (decay != nullptr),
                "b200_linear_recurrence: give either gate pre-activations or a decay per head");
+  B200_REQUIRE(!gates || aux, "b200_linear_recurrence: the gated form returns (n . q, m) in aux");
   B200_REQUIRE(batch > 0 && H > 0 && D > 0 && E > 0 && D <= kRecRows * 32 && (act == 0 || act == 1),
                "b200_linear_recurrence: heads %d, key size %d (max %d), value size %d", H, D,
                kRecRows * 32, E);
+  B200_REQUIRE(ld_state % 2 == 0 && (reinterpret_cast<uintptr_t>(state) & 7) == 0,
+               "b200_linear_recurrence: the state rows must be 8-byte aligned");
   const int P = rec_parts(D);
-  const int ES = kRecThreads / P;
-  const size_t smem = static_cast<size_t>(kRecChunk) * (2 * D + ES + 2) * sizeof(float);
-  B200_REQUIRE(smem <= 200 * 1024, "b200_linear_recurrence: key size %d too large", D);
+  const int ES = 2 * (kRecThreads / P);
+  const size_t esz = dtype == B200_F32 ? 4 : 2;
+  // rows stream through cp.async in 8-byte pieces when every piece is aligned
+  const int pe = static_cast<int>(8 / esz);
+  const bool stream_rows = D % pe == 0 && E % pe == 0 && ldq % pe == 0 && ldk % pe == 0 && ldv % pe == 0 &&
+                           (reinterpret_cast<uintptr_t>(q) & 7) == 0 && (reinterpret_cast<uintptr_t>(k) & 7) == 0 &&
+                           (reinterpret_cast<uintptr_t>(v) & 7) == 0;
+  auto smem_for = [&](int ch) {
+    return sizeof(float) * (static_cast<size_t>(ch) * (2 * P * kRecRows + ES) + 5 * kRecChunk) +
+           (stream_rows ? 2 * esz * ch * (2 * D + ES) : 0);
+  };
+  int CH = kRecChunk;
+  while (CH > 4 && smem_for(CH) > 100 * 1024) CH >>= 1;   // two CTAs per SM
+  const size_t smem = smem_for(CH);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   ScopedKernelTimer timer("linear_recurrence", st);
-  const dim3 grid(ceil_div(E, ES), H, batch);
+  const dim3 grid(ceil_div(E + (gates ? 1 : 0), ES), H, batch);
+  B200_REQUIRE(H <= 65535 && batch <= 65535, "b200_linear_recurrence: grid too large");
 #define LAUNCH(TT, G)                                                                                \
   do {                                                                                               \
     auto kern = linear_recurrence_kernel<TT, G>;                                                     \
@@ -210,8 +326,8 @@ extern "C" int b200_linear_recurrence(const void* q, int64_t ldq, const void* k,
                                         static_cast<int>(smem)));                                    \
     launch_kernel(kern, grid, dim3(kRecThreads), smem, st, 1, 0, static_cast<const TT*>(q), ldq,     \
                   static_cast<const TT*>(k), ldk, static_cast<const TT*>(v), ldv, gates, ldg, decay, \
-                  cap, q_scale, den_eps, act, state, ld_state, slot, tok_pos, ext_start, ext_len,    \
-                  out, ldo, H, D, E, P);                                                             \
+                  cap, q_scale, act, state, ld_state, slot, tok_pos, ext_start, ext_len, out, ldo,   \
+                  aux, ld_aux, H, D, E, P, CH, stream_rows ? 1 : 0);                                 \
   } while (0)
 #define BY_G(TT)                  \
   do {                            \
@@ -228,18 +344,23 @@ extern "C" int b200_linear_recurrence(const void* q, int64_t ldq, const void* k,
   return 0;
 }
 
+// aux (optional): fp32 [T, 2 H] = (n . q, m) of the gated recurrence; o is divided by
+// max(|n . q|, exp(-m)) + den_eps per (token, head) before the norm
 extern "C" int b200_gated_group_rmsnorm(const float* o, int64_t ldo, const float* w, const void* z,
                                         int64_t ldz, void* out, int64_t ldout, int T, int N,
-                                        int group, float eps, int dtype, void* stream) {
+                                        int group, float eps, const float* aux, int64_t ld_aux, int H,
+                                        float den_eps, int dtype, void* stream) {
   using namespace b200;
   if (T == 0) return 0;
   B200_REQUIRE(o && out && T > 0 && N > 0 && group > 0 && N % group == 0,
                "b200_gated_group_rmsnorm: %d coordinates in groups of %d", N, group);
+  B200_REQUIRE(!aux || (H > 0 && N % H == 0), "b200_gated_group_rmsnorm: %d coordinates, %d heads", N, H);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   ScopedKernelTimer timer("gated_group_rmsnorm", st);
 #define LAUNCH(TT)                                                                                   \
   launch_kernel(gated_group_rmsnorm_kernel<TT, TT>, dim3(T), dim3(256), 0, st, 1, 0, o, ldo, w,      \
-                static_cast<const TT*>(z), ldz, static_cast<TT*>(out), ldout, N, group, eps)
+                static_cast<const TT*>(z), ldz, static_cast<TT*>(out), ldout, N, group, eps, aux,    \
+                ld_aux, H, den_eps)
   if (dtype == B200_BF16) LAUNCH(__nv_bfloat16);
   else if (dtype == B200_F16) LAUNCH(__half);
   else if (dtype == B200_F32) LAUNCH(float);

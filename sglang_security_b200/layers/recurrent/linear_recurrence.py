@@ -37,10 +37,12 @@ def state_width(heads: int, dim: int, vdim: int, gated: bool) -> int:
 def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int, dim: int, vdim: int,
                       state: torch.Tensor, fb, gates: Optional[torch.Tensor] = None,
                       decay: Optional[torch.Tensor] = None, cap: float = 0.0, q_scale: float = 1.0,
-                      den_eps: float = 1e-6, silu: bool = False) -> torch.Tensor:
+                      silu: bool = False):
     """q, k [T, heads * dim], v [T, heads * vdim] (row-strided views are fine) -> fp32 [T, heads * vdim].
-    `gates` fp32 [T, 2 * heads] (input then forget pre-activations) selects the gated form, `decay`
-    fp32 [heads] the constant one.  `fb` carries tok_pos / ext_start / ext_len / req_pool_indices."""
+    `decay` fp32 [heads] selects the constant form.  `gates` fp32 [T, 2 * heads] (input then forget
+    pre-activations) selects the gated form, which returns (o, aux): o un-normalised and aux fp32
+    [T, 2 * heads] = (n . q, m) per head, for the division by max(|n . q|, exp(-m)) + den_eps that
+    `gated_group_rmsnorm` performs.  `fb` carries tok_pos / ext_start / ext_len / req_pool_indices."""
     if not q.is_cuda:
         raise _lib.B200Error("linear_recurrence: tensors must live on a CUDA device (no CPU path)")
     for t in (q, k, v):
@@ -48,29 +50,34 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: 
             raise _lib.B200Error("linear_recurrence: q, k, v need contiguous rows of one dtype")
     T = q.shape[0]
     out = torch.empty((T, heads * vdim), dtype=torch.float32, device=q.device)
+    aux = torch.empty((T, 2 * heads), dtype=torch.float32, device=q.device) if gates is not None else None
     if gates is not None and (gates.dtype != torch.float32 or gates.stride(-1) != 1):
         raise _lib.B200Error("linear_recurrence: gate pre-activations must be fp32 rows")
     rc = _lib.load().b200_linear_recurrence(
         q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
         _lib.ptr(gates), gates.stride(0) if gates is not None else 0, _lib.ptr(decay), float(cap),
-        float(q_scale), float(den_eps), 1 if silu else 0, state.data_ptr(), state.stride(0),
+        float(q_scale), 1 if silu else 0, state.data_ptr(), state.stride(0),
         fb.req_pool_indices.data_ptr(), fb.tok_pos.data_ptr(), fb.ext_start.data_ptr(),
-        fb.ext_len.data_ptr(), out.data_ptr(), out.stride(0), int(fb.batch_size), heads, dim, vdim,
-        _lib.dtype_code(q.dtype), _lib.current_stream())
+        fb.ext_len.data_ptr(), out.data_ptr(), out.stride(0), _lib.ptr(aux), 2 * heads,
+        int(fb.batch_size), heads, dim, vdim, _lib.dtype_code(q.dtype), _lib.current_stream())
     _lib.check(rc, "b200_linear_recurrence")
-    return out
+    return out if aux is None else (out, aux)
 
 
 def gated_group_rmsnorm(o: torch.Tensor, weight: Optional[torch.Tensor], z: Optional[torch.Tensor],
-                        group: int, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
-    """o fp32 [T, N] -> o / rms over groups of `group` coordinates * weight * sigmoid(z), in out_dtype."""
+                        group: int, eps: float, out_dtype: torch.dtype, aux: Optional[torch.Tensor] = None,
+                        heads: int = 0, den_eps: float = 1e-6) -> torch.Tensor:
+    """o fp32 [T, N] -> o / rms over groups of `group` coordinates * weight * sigmoid(z), in out_dtype.
+    With `aux` (the gated recurrence's (n . q, m), fp32 [T, 2 * heads]) each head of o is first divided
+    by max(|n . q|, exp(-m)) + den_eps."""
     T, N = o.shape
     if z is not None and (z.dtype != out_dtype or z.stride(-1) != 1):
         raise _lib.B200Error("gated_group_rmsnorm: the gate must have the output dtype and contiguous rows")
     out = torch.empty((T, N), dtype=out_dtype, device=o.device)
     rc = _lib.load().b200_gated_group_rmsnorm(
         o.data_ptr(), o.stride(0), _lib.ptr(weight), _lib.ptr(z), z.stride(0) if z is not None else 0,
-        out.data_ptr(), out.stride(0), T, N, int(group), float(eps), _lib.dtype_code(out_dtype),
+        out.data_ptr(), out.stride(0), T, N, int(group), float(eps), _lib.ptr(aux),
+        aux.stride(0) if aux is not None else 0, int(heads), float(den_eps), _lib.dtype_code(out_dtype),
         _lib.current_stream())
     _lib.check(rc, "b200_gated_group_rmsnorm")
     return out
@@ -121,10 +128,10 @@ class MLSTMMixer(_MatrixMemoryMixer):
     def forward(self, h: torch.Tensor, x32: torch.Tensor, fb) -> torch.Tensor:
         q, k, v, g = self._split(h)
         gates = F.linear(x32, self.gate_weight, self.gate_bias)
-        o = linear_recurrence(q, k, v, self.heads, self.dim, self.vdim, fb.state_pool.get(self.layer_id), fb,
-                              gates=gates, cap=self.gate_cap, q_scale=self.dim ** -0.5,
-                              den_eps=self.den_eps)
-        y = gated_group_rmsnorm(o, self.norm_weight, g, self.vdim, self.eps, self.params_dtype)
+        o, aux = linear_recurrence(q, k, v, self.heads, self.dim, self.vdim, fb.state_pool.get(self.layer_id),
+                                   fb, gates=gates, cap=self.gate_cap, q_scale=self.dim ** -0.5)
+        y = gated_group_rmsnorm(o, self.norm_weight, g, self.vdim, self.eps, self.params_dtype, aux=aux,
+                                heads=self.heads, den_eps=self.den_eps)
         out, _ = self.o_proj(y)
         return out
 

@@ -1,6 +1,7 @@
-"""Prefill and decode throughput of the Desirax design at layer sizes that resemble a real model's,
-beside the Llama-family decoder stack of this package at equal width / heads / head size / layer count
-and equal active feed-forward size (random weights, bf16).  Driven by `bench.py --arch-compare`.
+"""Prefill and decode throughput of the Desirax and Dozetar designs at layer sizes that resemble a real
+model's, beside the Llama-family decoder stack of this package at equal width / heads / head size /
+layer count and equal active feed-forward size (random weights, bf16).  Driven by
+`bench.py --arch-compare` (sizes named "dz-..." are Dozetar's).
 
 Timing: CUDA events on the launching stream around whole engine steps, after warm-up steps; every step
 touches more weight and cache bytes than L2 holds at the larger size.  Per-kernel times come from the
@@ -24,7 +25,33 @@ SIZES = {
     "w2048-moe": dict(width=2048, heads=16, dim=64, rot=64, vdim=128, kv_rank=512, q_rank=768, window=4096,
                       layers=4, ff=5120, moe=dict(experts=32, top=4, ff=1024, shared=1024), vocab=32000),
 }
+# Dozetar: layers alternate the gated matrix-memory mixer and the parallel (attention | decayed
+# linear attention) mixer; every layer has experts.  `ff` is the Llama-like stack's dense size = the
+# active expert size top * expert_ff.
+DOZETAR_SIZES = {
+    "dz-w1024": dict(width=1024, layers=4, vocab=32000, heads=8, kv_heads=2, dim=128, vdim=128, window=1024,
+                     keep_first=4, rot=64, m_heads=8, m_dim=64, m_vdim=128, r_heads=8, r_dim=64, r_vdim=128,
+                     experts=16, top=2, expert_ff=1024, ff=2048, rot_llama=0),
+    "dz-w2048": dict(width=2048, layers=4, vocab=32000, heads=16, kv_heads=4, dim=128, vdim=128, window=4096,
+                     keep_first=4, rot=64, m_heads=16, m_dim=128, m_vdim=128, r_heads=16, r_dim=64, r_vdim=128,
+                     experts=32, top=4, expert_ff=1024, ff=4096, rot_llama=0),
+}
 WORK = dict(prefill_reqs=4, prefill_len=2048, decode_bs=32, decode_ctx=2048)
+
+
+def _dozetar_cfg(s):
+    mlstm = {"type": "mlstm", "mixer": {"heads": s["m_heads"], "dim": s["m_dim"], "vdim": s["m_vdim"], "gate_cap": 15.0}}
+    par = {"type": "parallel", "mixer": {
+        "left": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"],
+                 "scale": s["dim"] ** -0.5, "mask": {"size": s["window"], "keep_first": s["keep_first"]},
+                 "rot": {"base": 1e6, "dims": s["rot"]}},
+        "right": {"heads": s["r_heads"], "dim": s["r_dim"], "vdim": s["r_vdim"],
+                  "decay": [1.0 - 2.0 ** (-3 - 5 * i / max(1, s["r_heads"] - 1)) for i in range(s["r_heads"])]},
+        "left_scale": 0.7, "right_scale": 0.7}}
+    f = {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"]}, "expert": {"ff": s["expert_ff"]}}
+    return {"architecture": "Dozetar", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "residual_mult": 0.5, "logit_softcap": 30.0,
+            "layers": [dict(mlstm if i % 2 == 0 else par, mlp=f) for i in range(s["layers"])]}
 
 
 def _desirax_cfg(s):
@@ -169,6 +196,94 @@ def bench_desirax(name, s, steps, warmup, device="cuda"):
     return row
 
 
+def bench_dozetar(name, s, steps, warmup, device="cuda"):
+    from ..configs.dozetar import dozetar_config
+    from ..managers.schedule_batch import Req, StepItem
+    from ..managers.scheduler import Scheduler
+    from ..models.registry import resolve_model_cls
+    from .model_runner import ModelRunner
+
+    cfg = dozetar_config(_dozetar_cfg(s))
+    torch.manual_seed(0)
+    with torch.device(device):
+        model = resolve_model_cls("Dozetar")(cfg, params_dtype=torch.bfloat16)
+    for n_, p in model.named_parameters():
+        if n_.endswith("norm_weight") or n_.endswith("norm1.weight") or n_.endswith("norm2.weight"):
+            p.data.fill_(1.0)
+        elif n_.endswith("gate_bias"):
+            p.data.fill_(1.0)
+        elif n_.endswith("sink") or n_.endswith("bias"):
+            p.data.zero_()
+        else:
+            p.data.normal_(0, 0.02)
+    W = WORK
+    bs = max(W["prefill_reqs"], W["decode_bs"])
+    tokens = W["decode_bs"] * (W["decode_ctx"] + 64) + W["prefill_reqs"] * W["prefill_len"]
+    runner = ModelRunner(None, torch.bfloat16, max_total_tokens=tokens, max_running_requests=bs + 1,
+                         context_length=max(W["prefill_len"], W["decode_ctx"] + 64), device=device,
+                         model=model.eval(), model_config=SimpleNamespace(architecture="Dozetar", hf_config=cfg))
+    sched = Scheduler(runner)
+    g = torch.Generator().manual_seed(1)
+    rnd = lambda n: torch.randint(0, s["vocab"], (n,), generator=g).tolist()
+
+    def prefill():
+        reqs = [Req(rid=f"p{i}", input_ids=rnd(W["prefill_len"])) for i in range(W["prefill_reqs"])]
+        for r in reqs:
+            assert runner.admit(r)
+        sched.run_step([StepItem(r, r.input_ids, want=[len(r.input_ids) - 1]) for r in reqs])
+        for r in reqs:
+            runner.release(r)
+
+    names = ["linear_recurrence", "gated_group_rmsnorm", "sink_attn", "attn_extend", "qk_norm_rope_write",
+             "moe_grouped_gemm", "moe_route", "moe_align", "add_normed", "softcap_rows"]
+    row = {"arch": "dozetar", "size": name}
+    ms = _timed(prefill, steps, warmup)
+    ntok = W["prefill_reqs"] * W["prefill_len"]
+    row["prefill_ms"], row["prefill_tokens_per_s"] = round(ms, 3), round(ntok / ms * 1e3)
+    row["prefill_kernels"] = _kernel_times(prefill, names)
+    reqs = [Req(rid=f"d{i}", input_ids=rnd(W["decode_ctx"])) for i in range(W["decode_bs"])]
+    for r in reqs:
+        assert runner.admit(r)
+    for i in range(0, len(reqs), 4):
+        sched.run_step([StepItem(r, r.input_ids) for r in reqs[i:i + 4]])
+    state = {"n": 0}
+
+    def decode():
+        state["n"] += 1
+        assert state["n"] < 60
+        sched.run_step([StepItem(r, [7], want=[0]) for r in reqs])
+
+    ms = _timed(decode, steps, warmup)
+    row["decode_ms"], row["decode_tokens_per_s"] = round(ms, 3), round(W["decode_bs"] / ms * 1e3)
+    row["decode_kernels"] = _kernel_times(decode, names)
+
+    def mixed():
+        state["n"] += 1
+        assert state["n"] < 60
+        new = Req(rid=f"m{state['n']}", input_ids=rnd(512))
+        assert runner.admit(new)
+        sched.run_step([StepItem(r, [7], want=[0]) for r in reqs] + [StepItem(new, new.input_ids, want=[511])])
+        runner.release(new)
+
+    row["mixed_ms"] = round(_timed(mixed, min(steps, 8), 3), 3)
+    # algorithmic work of one launch (all tokens, one layer)
+    L, U = W["prefill_len"], W["prefill_reqs"]
+    keys = sum(min(p + 1, s["window"]) + min(s["keep_first"], max(0, p + 1 - s["window"])) for p in range(L)) * U
+    row["attn_prefill_flops"] = 2 * keys * s["heads"] * (s["dim"] + s["vdim"])
+    keys_d = W["decode_bs"] * (min(W["decode_ctx"] + 1, s["window"]) + s["keep_first"])
+    row["attn_decode_bytes"] = keys_d * s["kv_heads"] * (s["dim"] + s["vdim"]) * 2
+    # recurrences: 3 fp32 multiply-adds per state element and token (decay, outer product, read-out); a
+    # decoded token reads and writes its state once
+    row["mlstm_prefill_fma"] = 3 * U * L * s["m_heads"] * s["m_dim"] * s["m_vdim"]
+    row["decayed_prefill_fma"] = 3 * U * L * s["r_heads"] * s["r_dim"] * s["r_vdim"]
+    row["mlstm_decode_bytes"] = 2 * 4 * W["decode_bs"] * s["m_heads"] * s["m_dim"] * s["m_vdim"]
+    row["decayed_decode_bytes"] = 2 * 4 * W["decode_bs"] * s["r_heads"] * s["r_dim"] * s["r_vdim"]
+    row["expert_prefill_flops"] = 2 * 2 * U * L * s["top"] * s["expert_ff"] * s["width"]
+    del runner, sched, model
+    torch.cuda.empty_cache()
+    return row
+
+
 def bench_llama_like(name, s, steps, warmup, device="cuda"):
     """The package's Llama-family stack (B200DecoderLayer: fused RMSNorm, rotary + KV write, paged
     attention, gated silu MLP) at the same width, heads, head size 128, layers, GQA 4:1, bf16."""
@@ -176,7 +291,7 @@ def bench_llama_like(name, s, steps, warmup, device="cuda"):
     from .forward_batch_info import ForwardBatch, ForwardMode
 
     W = WORK
-    hd = s["dim"] + s["rot"]
+    hd = s["dim"] + s.get("rot_llama", s["rot"])
     geo = ModelGeometry(name, s["width"], s["heads"], max(1, s["heads"] // 4), hd, s["ff"], s["layers"],
                         s["vocab"], 1e6, False)
     bs = W["decode_bs"]
@@ -231,10 +346,10 @@ def bench_llama_like(name, s, steps, warmup, device="cuda"):
 
 def run(steps: int, warmup: int, sizes=None):
     rows = []
-    for name, s in SIZES.items():
+    for name, s in list(SIZES.items()) + list(DOZETAR_SIZES.items()):
         if sizes and name not in sizes:
             continue
-        for fn in (bench_desirax, bench_llama_like):
+        for fn in ((bench_dozetar if name in DOZETAR_SIZES else bench_desirax), bench_llama_like):
             t0 = time.time()
             row = fn(name, s, steps, warmup)
             row["wall_s"] = round(time.time() - t0, 1)

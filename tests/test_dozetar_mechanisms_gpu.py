@@ -50,6 +50,19 @@ def test_softcap_rows():
     assert torch.equal(softcap(z.to(DEV).bfloat16(), 0.0).cpu(), z.bfloat16().float())
 
 
+def test_gated_group_rmsnorm_divides_by_the_recurrence_normaliser():
+    from sglang_security_b200.layers.recurrent.linear_recurrence import gated_group_rmsnorm
+
+    g = torch.Generator().manual_seed(3)
+    T, H, E = 6, 3, 10
+    o, w = torch.randn(T, H * E, generator=g), 1 + 0.3 * torch.randn(H * E, generator=g)
+    aux = torch.cat([torch.randn(T, H, generator=g) * 3, torch.randn(T, H, generator=g)], 1)
+    got = gated_group_rmsnorm(o.to(DEV), w.to(DEV), None, E, 1e-4, torch.float32, aux=aux.to(DEV), heads=H, den_eps=1e-6)
+    den = torch.maximum(aux[:, :H].abs(), torch.exp(-aux[:, H:])).double() + 1e-6
+    y = P.rms(o.double().view(T, H, E) / den[:, :, None], 1e-4).reshape(T, H * E) * w.double()
+    assert _err(got, y) <= 1e-5
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,vdim,whole", [(3, 20, False), (3, 20, True), (1, 7, False), (9, 64, True)])
 def test_gated_group_rmsnorm(dtype, heads, vdim, whole):
@@ -90,6 +103,10 @@ def _run_recurrence(gated, H, D, E, lens, cuts, dtype, seed=0, cap=6.0, reuse=Fa
         out = linear_recurrence(part[0], part[1], part[2], H, D, E, state, fb,
                                 gates=part[3] if gated else None, decay=None if gated else decay.to(DEV),
                                 cap=cap, q_scale=D ** -0.5 if gated else 1.0, silu=not gated)
+        if gated:          # (un-normalised o, (n . q, m)): the division the norm kernel fuses, done here
+            num, aux = out
+            den = torch.maximum(aux[:, :H].abs(), torch.exp(-aux[:, H:])) + 1e-6
+            out = (num.view(-1, H, E) / den[:, :, None]).view(-1, H * E)
         o = 0
         for i, n in entries:
             got[i].append(out[o:o + n].cpu())
@@ -139,7 +156,7 @@ def test_recurrence_state_of_a_reused_slot_is_ignored():
         q, k, v = (torch.randn(9, H * D, generator=torch.Generator().manual_seed(7)).to(DEV) for _ in range(3))
         gates = torch.randn(9, 2 * H, generator=torch.Generator().manual_seed(8)).to(DEV)
         fb = hb.step([(0, 9)])
-        outs.append(linear_recurrence(q, k, v, H, D, E, state, fb, gates=gates, cap=0.0))
+        outs.append(torch.cat(linear_recurrence(q, k, v, H, D, E, state, fb, gates=gates, cap=0.0), 1))
         hb.release(0)                     # the next sequence in this row starts at position 0
     assert torch.equal(outs[0], outs[1]) and state.abs().max() > 0
 
