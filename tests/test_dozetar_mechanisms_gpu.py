@@ -144,6 +144,23 @@ def test_recurrence_bf16_inputs_and_long_decode(gated):
     assert _err(got[0], want[0]) <= 1e-4
 
 
+@pytest.mark.parametrize("gated", [False, True])
+def test_recurrence_cta_sizes_share_one_state_layout(gated):
+    """A few long portions split a head's columns over several CTAs, a wide batch of decoded tokens gives
+    each head one large CTA: the state one launch leaves must be the state the other reads."""
+    from sglang_security_b200 import _lib
+
+    H, D, E, B = 8, 64, 128, 24
+    cuts = [[12] + [1] * 3 for _ in range(B)]
+    got, want = _run_recurrence(gated, H, D, E, [15] * B, cuts, torch.float32, seed=9)
+    wide = _lib.last_variant()                      # the last step: 24 single tokens side by side
+    for a, b in zip(got, want):
+        assert _err(a, b) <= 5e-5
+    one, _ = _run_recurrence(gated, H, D, E, [15], [[12, 1, 1, 1]], torch.float32, seed=9)
+    assert _lib.last_variant() != wide
+    assert _err(one[0], want[0]) <= 5e-5
+
+
 def test_recurrence_state_of_a_reused_slot_is_ignored():
     from sglang_security_b200.layers.recurrent.linear_recurrence import linear_recurrence, state_width
 
