@@ -663,12 +663,13 @@ int b200_qk_norm_rope_write(const void* q, int64_t ldq, const void* k, int64_t l
 /* Step 2: token t at position p of request req_idx[tok_b[t]] sees keys j <= p with p - j < window
  * (window 0: all) or j < keep_first; weights = exp(score) / (sum exp(score) + exp(sink[h])) (sink
  * NULL: plain softmax); out [T, H * E] in the pool's dtype.  With tok_list (T row numbers) only
- * those rows of q / out are done.                                                                  */
+ * those rows of q / out are done.  max_keys: the longest key list of the launch (a hint that sizes
+ * the CTA; 0 = unknown).                                                                           */
 int b200_sink_attn(const float* q, int64_t ldq, const void* pool, int64_t ld_pool, int k_off,
                    int v_off, const int* req_to_token, int64_t ld_r2t, const int64_t* req_idx,
                    const int* tok_pos, const int* tok_b, const float* sink, float scale, int window,
                    int keep_first, void* out, int64_t ldo, int T, int H, int G, int D, int E,
-                   const int* tok_list, int dtype, void* stream);
+                   const int* tok_list, int max_keys, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -211,7 +211,7 @@ _SIGNATURES = {
                                         c_void_p]),
     "b200_sink_attn": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_int64,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p,
-                               c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
+                               c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p]),
 }
 
 

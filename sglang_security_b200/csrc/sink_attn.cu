@@ -121,11 +121,11 @@ qk_norm_rope_write_kernel(const T* __restrict__ q, int64_t ldq, const T* __restr
     prow[v_off + i] = from_float<TP>(to_float<T>(vr[i]));
 }
 
-constexpr int kSinkWarps = 4;
+constexpr int kSinkMaxWarps = 16;  // warps per CTA: 4 to 16, by the longest key list (host)
 constexpr int kSinkMaxCols = 8;    // value size <= 256
 
 template <typename TP, typename TO>
-__global__ void __launch_bounds__(kSinkWarps * 32)
+__global__ void __launch_bounds__(kSinkMaxWarps * 32)
 sink_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __restrict__ pool,
                  int64_t ld_pool, int k_off, int v_off, const int* __restrict__ req_to_token,
                  int64_t ld_r2t, const int64_t* __restrict__ req_idx, const int* __restrict__ tok_pos,
@@ -133,6 +133,7 @@ sink_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __restrict_
                  int keep_first, TO* __restrict__ out, int64_t ldo, int H, int G, int D, int E,
                  const int* __restrict__ tok_list) {
   extern __shared__ float sink_smem[];       // q [D], then per warp: acc [E], m, l
+  const int kSinkWarps = blockDim.x >> 5;
   float* qs = sink_smem;
   float* wacc = qs + D;
   float* wm = wacc + kSinkWarps * E;
@@ -152,6 +153,9 @@ sink_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __restrict_
   for (int c = 0; c < kSinkMaxCols; ++c) acc[c] = 0.f;
   const bool vec = (D % 8 == 0) && sizeof(TP) == 2 && (ld_pool % 8 == 0) && ((k_off + g * D) % 8 == 0) &&
                    ((reinterpret_cast<uintptr_t>(pool) & 15) == 0);
+  // values: 4 consecutive columns per lane with vector loads when every piece is aligned
+  const bool vblk = (E % 4 == 0) && (ld_pool % 4 == 0) && ((v_off + g * E) % 4 == 0) &&
+                    ((reinterpret_cast<uintptr_t>(pool) & 15) == 0);
   for (int n0 = warp * 32; n0 < nkeys; n0 += kSinkWarps * 32) {
     const int n = n0 + lane;
     int64_t slot = 0;
@@ -163,6 +167,7 @@ sink_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __restrict_
       float s0 = 0.f, s1 = 0.f;
       bool done = false;
       if constexpr (sizeof(TP) == 2) {
+#pragma unroll 4
         for (int d = 0; vec && d < D; d += 8) {
           const uint4 u = *reinterpret_cast<const uint4*>(kr + d);
           const TP* e8 = reinterpret_cast<const TP*>(&u);
@@ -198,14 +203,40 @@ sink_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __restrict_
 #pragma unroll
     for (int c = 0; c < kSinkMaxCols; ++c) acc[c] *= corr;
     const int cnt = min(32, nkeys - n0);
-    for (int jj = 0; jj < cnt; ++jj) {
+    // unrolled so that the value rows of several keys are in flight at once (a rolled loop waits a
+    // full memory round trip per key)
+#pragma unroll 8
+    for (int jj = 0; jj < 32; ++jj) {
+      if (jj >= cnt) break;
       const float pw = __shfl_sync(0xffffffffu, pj, jj);
       const int64_t sl = __shfl_sync(0xffffffffu, slot, jj);
       const TP* vr = pool + sl * ld_pool + v_off + g * E;
+      if (vblk) {
+        // a lane owns 4 consecutive columns per 128: one 8-byte (16-bit pool) or 16-byte load each
 #pragma unroll
-      for (int c = 0; c < kSinkMaxCols; ++c) {
-        const int e = lane + 32 * c;
-        if (e < E) acc[c] = fmaf(pw, to_float<TP>(vr[e]), acc[c]);
+        for (int c = 0; c < kSinkMaxCols / 4; ++c) {
+          const int e = 128 * c + 4 * lane;
+          if (e < E) {
+            float x[4];
+            if constexpr (sizeof(TP) == 2) {
+              const uint2 u = *reinterpret_cast<const uint2*>(vr + e);
+              const TP* t4 = reinterpret_cast<const TP*>(&u);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) x[i] = to_float<TP>(t4[i]);
+            } else {
+              const float4 u = *reinterpret_cast<const float4*>(vr + e);
+              x[0] = u.x, x[1] = u.y, x[2] = u.z, x[3] = u.w;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[4 * c + i] = fmaf(pw, x[i], acc[4 * c + i]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < kSinkMaxCols; ++c) {
+          const int e = lane + 32 * c;
+          if (e < E) acc[c] = fmaf(pw, to_float<TP>(vr[e]), acc[c]);
+        }
       }
     }
   }
@@ -215,24 +246,24 @@ sink_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __restrict_
   }
 #pragma unroll
   for (int c = 0; c < kSinkMaxCols; ++c) {
-    const int e = lane + 32 * c;
+    const int e = vblk ? 128 * (c / 4) + 4 * lane + (c & 3) : lane + 32 * c;
     if (e < E) wacc[warp * E + e] = acc[c];
   }
   __syncthreads();
   float mt = sink ? sink[h] : -INFINITY;
-#pragma unroll
   for (int w = 0; w < kSinkWarps; ++w) mt = fmaxf(mt, wm[w]);
   float lt = sink ? expf(sink[h] - mt) : 0.f;
-  float f[kSinkWarps];
+  float f[kSinkMaxWarps];
 #pragma unroll
-  for (int w = 0; w < kSinkWarps; ++w) {
-    f[w] = wm[w] == -INFINITY ? 0.f : expf(wm[w] - mt);
-    lt = fmaf(wl[w], f[w], lt);
+  for (int w = 0; w < kSinkMaxWarps; ++w) {
+    f[w] = (w < kSinkWarps && wm[w] != -INFINITY) ? expf(wm[w] - mt) : 0.f;
+    if (w < kSinkWarps) lt = fmaf(wl[w], f[w], lt);
   }
   for (int e = threadIdx.x; e < E; e += kSinkWarps * 32) {
     float o = 0.f;
 #pragma unroll
-    for (int w = 0; w < kSinkWarps; ++w) o = fmaf(wacc[w * E + e], f[w], o);
+    for (int w = 0; w < kSinkMaxWarps; ++w)
+      if (w < kSinkWarps) o = fmaf(wacc[w * E + e], f[w], o);
     out[t * ldo + h * E + e] = from_float<TO>(o / lt);
   }
 }
@@ -283,7 +314,7 @@ extern "C" int b200_sink_attn(const float* q, int64_t ldq, const void* pool, int
                               const int64_t* req_idx, const int* tok_pos, const int* tok_b,
                               const float* sink, float scale, int window, int keep_first, void* out,
                               int64_t ldo, int T, int H, int G, int D, int E, const int* tok_list,
-                              int dtype, void* stream) {
+                              int max_keys, int dtype, void* stream) {
   using namespace b200;
   if (T == 0) return 0;
   B200_REQUIRE(q && pool && req_to_token && req_idx && tok_pos && tok_b && out,
@@ -292,6 +323,9 @@ extern "C" int b200_sink_attn(const float* q, int64_t ldq, const void* pool, int
                    window >= 0 && keep_first >= 0,
                "b200_sink_attn: heads %d / %d, key size %d, value size %d (max %d)", H, G, D, E,
                32 * kSinkMaxCols);
+  // one warp per 64 keys of the longest list (a hint; 0 = unknown): a warp's tiles are dependent round
+  // trips to memory (slots, keys, values), so long lists want many warps and short ones few
+  const int kSinkWarps = max_keys <= 0 ? 4 : min(kSinkMaxWarps, max(4, ceil_div(max_keys, 64)));
   const size_t smem = sizeof(float) * (D + kSinkWarps * (E + 2));
   B200_REQUIRE(smem <= 48 * 1024, "b200_sink_attn: key size %d too large", D);
   cudaStream_t st = static_cast<cudaStream_t>(stream);

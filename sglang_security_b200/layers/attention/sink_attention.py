@@ -142,7 +142,8 @@ class SinkAttention(nn.Module):
                 q32.data_ptr(), q32.stride(0), pool.data_ptr(), pool.stride(0), 0, G * D, r2t.data_ptr(),
                 r2t.stride(0), fb.req_pool_indices.data_ptr(), fb.tok_pos.data_ptr(), fb.tok_b.data_ptr(),
                 _lib.ptr(self.sink), self.scale, self.window, self.keep_first, out.data_ptr(), out.stride(0),
-                n_core, H, G, D, E, _lib.ptr(plan["rest"]) if plan is not None else None, code, st)
+                n_core, H, G, D, E, _lib.ptr(plan["rest"]) if plan is not None else None,
+                min(fb.max_seq_len, self.window + self.keep_first) if self.window else fb.max_seq_len, code, st)
             _lib.check(rc, "b200_sink_attn")
         res, _ = self.o_proj(out)
         return res

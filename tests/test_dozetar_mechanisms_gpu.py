@@ -220,7 +220,7 @@ def _attend(q, k, v, sink, scale, window, keep_first, cuts, dtype, page=16, seed
         rc = lib.b200_sink_attn(q32.data_ptr(), q32.stride(0), pool.data_ptr(), pool.stride(0), 0, G * D,
                                 fb.req_to_token.data_ptr(), fb.req_to_token.stride(0), fb.req_pool_indices.data_ptr(),
                                 fb.tok_pos.data_ptr(), fb.tok_b.data_ptr(), _lib.ptr(sink_d),
-                                scale, window or 0, keep_first, out.data_ptr(), out.stride(0), n, H, G, D, E, None, code, 0)
+                                scale, window or 0, keep_first, out.data_ptr(), out.stride(0), n, H, G, D, E, None, at + n if seed % 2 == 0 else 0, code, 0)
         _lib.check(rc, "attn")
         torch.cuda.synchronize()
         outs.append(out.cpu())
