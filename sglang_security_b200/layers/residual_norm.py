@@ -5,8 +5,9 @@
     x += mult * y / sqrt(mean(y^2) + eps) * weight
 
 `AddNormed` owns the weight; one launch does the sum, the norm, the add and, on request, the copy of
-the new residual in the model dtype that the next sublayer's matrix products read.  `softcap` is the
-logit cap cap * tanh(z / cap) with a fp32 result."""
+the new residual in the model dtype that the next sublayer's matrix products read.  `ResidualRMSNorm`
+is the plain RMS norm of the fp32 residual with a per-coordinate weight (a model's final norm), its
+output in the model dtype.  `softcap` is the logit cap cap * tanh(z / cap) with a fp32 result."""
 from __future__ import annotations
 
 from typing import Optional
@@ -51,6 +52,26 @@ class AddNormed(nn.Module):
             _lib.ptr(out), ld(out), t, w, _lib.dtype_code(dt), _lib.current_stream())
         _lib.check(rc, "b200_add_normed")
         return x if out_dtype == torch.float32 else out
+
+
+class ResidualRMSNorm(nn.Module):
+    def __init__(self, width: int, eps: float):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(width, dtype=torch.float32), requires_grad=False)
+        self.eps = float(eps)
+
+    def forward(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        """x fp32 [T, W] -> x / sqrt(mean(x^2) + eps) * weight in out_dtype (csrc/norm_shift.cu)."""
+        if not x.is_cuda or x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1:
+            raise _lib.B200Error("ResidualRMSNorm: a 2-D fp32 CUDA tensor with contiguous rows is expected")
+        t, w = x.shape
+        out = torch.empty((t, w), dtype=out_dtype, device=x.device)
+        rc = _lib.load().b200_scalar_rmsnorm_shift(
+            x.data_ptr(), x.stride(0), None, self.weight.data_ptr(), self.eps, None, None, 0, None, None, None,
+            None, None, out.data_ptr(), out.stride(0), None, 0, t, w, _lib.dtype_code(out_dtype),
+            _lib.current_stream())
+        _lib.check(rc, "b200_scalar_rmsnorm_shift")
+        return out
 
 
 def softcap(z: torch.Tensor, cap: float) -> torch.Tensor:

@@ -50,7 +50,7 @@ def _dozetar_cfg(s):
         "left_scale": 0.7, "right_scale": 0.7}}
     f = {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"]}, "expert": {"ff": s["expert_ff"]}}
     return {"architecture": "Dozetar", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
-            "residual_mult": 0.5, "logit_softcap": 30.0,
+            "residual_mult": 0.7, "logit_softcap": 50.0,
             "layers": [dict(mlstm if i % 2 == 0 else par, mlp=f) for i in range(s["layers"])]}
 
 
@@ -208,7 +208,8 @@ def bench_dozetar(name, s, steps, warmup, device="cuda"):
     with torch.device(device):
         model = resolve_model_cls("Dozetar")(cfg, params_dtype=torch.bfloat16)
     for n_, p in model.named_parameters():
-        if n_.endswith("norm_weight") or n_.endswith("norm1.weight") or n_.endswith("norm2.weight"):
+        if n_.endswith("norm_weight") or n_.endswith("norm1.weight") or n_.endswith("norm2.weight") or \
+                n_.endswith("final_norm.weight"):
             p.data.fill_(1.0)
         elif n_.endswith("gate_bias"):
             p.data.fill_(1.0)

@@ -12,7 +12,7 @@ sliding window, kept first tokens and a sink, beside a decayed linear attention)
 is a mixture of ungated squared-relu experts chosen by the largest sigmoid scores; a score
 multiplies its expert's input.  Norms, gates, recurrent state, attention scores, routers and the
 residual are fp32; the matrix products run in the model dtype.  Built from the shared layers
-AddNormed, MLSTMMixer / DecayedLinearAttention, SinkAttention, TopKRouter / ScaledInputExperts."""
+AddNormed / ResidualRMSNorm, MLSTMMixer / DecayedLinearAttention, SinkAttention, TopKRouter / ScaledInputExperts."""
 from __future__ import annotations
 
 import re
@@ -26,8 +26,7 @@ from ..layers.attention.sink_attention import SinkAttention
 from ..layers.linear import ColumnParallelLinear
 from ..layers.moe.fused_moe import ScaledInputExperts, TopKRouter
 from ..layers.recurrent.linear_recurrence import DecayedLinearAttention, MLSTMMixer
-from ..layers.residual_norm import AddNormed, softcap
-from ..layers.scalar_norm import _launch as _rmsnorm_rows
+from ..layers.residual_norm import AddNormed, ResidualRMSNorm, softcap
 from .registry import CacheSpec, register_model
 
 
@@ -83,7 +82,7 @@ class DozetarForCausalLM(nn.Module):
                                   requires_grad=False)
         self.layers = nn.ModuleList(DozetarLayer(config, s, i, params_dtype)
                                     for i, s in enumerate(config.layers))
-        self.final_norm_weight = nn.Parameter(torch.ones(config.width, dtype=torch.float32), requires_grad=False)
+        self.final_norm = ResidualRMSNorm(config.width, config.eps)
         self.head = ColumnParallelLinear(config.width, config.vocab, bias=False, params_dtype=params_dtype,
                                          tp_rank=0, tp_size=1)
 
@@ -111,10 +110,7 @@ class DozetarForCausalLM(nn.Module):
         return x
 
     def compute_logits(self, hidden_rows: torch.Tensor) -> torch.Tensor:
-        x = hidden_rows.contiguous()
-        h = torch.empty(x.shape, dtype=self.params_dtype, device=x.device)
-        _rmsnorm_rows(x, None, self.final_norm_weight, self.config.eps, None, None, None, None, h, None)
-        z, _ = self.head(h)
+        z, _ = self.head(self.final_norm(hidden_rows.contiguous(), self.params_dtype))
         return softcap(z, self.config.logit_softcap)
 
     # ---- weights -------------------------------------------------------------------------------
@@ -127,7 +123,7 @@ class DozetarForCausalLM(nn.Module):
             elif name == "head":
                 self.head.weight_loader(self.head.weight, w)
             elif name == "final.norm":
-                self.final_norm_weight.data.copy_(w.float())
+                self.final_norm.weight.data.copy_(w.float())
             else:
                 m = re.match(r"^l(\d+)\.(.+)$", name)
                 if not m or int(m.group(1)) >= len(self.layers):

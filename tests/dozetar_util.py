@@ -33,7 +33,7 @@ def experts(n=5, top=2, ff=24):
     return {"kind": "moe", "router": {"experts": n, "top": top}, "expert": {"ff": ff}}
 
 
-def config(layers: Sequence[tuple], vocab=97, width=40, eps=1e-5, mult=0.5, softcap: Optional[float] = 20.0) -> dict:
+def config(layers: Sequence[tuple], vocab=97, width=40, eps=1e-5, mult=0.6, softcap: Optional[float] = 20.0) -> dict:
     cfg = {"architecture": "Dozetar", "vocab": vocab, "width": width, "norm": {"eps": eps},
            "residual_mult": mult, "layers": [dict(m, mlp=f) for m, f in layers]}
     if softcap:

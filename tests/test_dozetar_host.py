@@ -16,7 +16,7 @@ def test_config_reads_every_size_and_constant():
 
     raw = _cfg()
     c = dozetar_config(raw)
-    assert (c.vocab, c.width, c.eps, c.residual_mult, c.logit_softcap) == (97, 40, 1e-5, 0.5, 20.0)
+    assert (c.vocab, c.width, c.eps, c.residual_mult, c.logit_softcap) == (97, 40, 1e-5, 0.6, 20.0)
     assert [L.type for L in c.layers] == ["mlstm", "parallel", "mlstm"]
     a = c.layers[1].mixer
     assert (a.left.heads, a.left.kv_heads, a.left.dim, a.left.vdim) == (4, 2, 16, 24)

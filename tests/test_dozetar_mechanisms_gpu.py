@@ -46,7 +46,7 @@ def test_softcap_rows():
     from sglang_security_b200.layers.residual_norm import softcap
 
     z = torch.linspace(-90, 90, 600).view(3, -1)
-    assert _err(softcap(z.to(DEV), 30.0), 30.0 * torch.tanh(z.double() / 30.0)) <= 1e-6
+    assert _err(softcap(z.to(DEV), 25.0), 25.0 * torch.tanh(z.double() / 25.0)) <= 1e-6
     assert torch.equal(softcap(z.to(DEV).bfloat16(), 0.0).cpu(), z.bfloat16().float())
 
 
@@ -235,7 +235,7 @@ def _qkv(T, H, G, D, E, seed, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,D,E,window,keep", [(4, 2, 16, 24, 9, 2), (6, 3, 64, 80, 40, 4), (2, 2, 8, 8, 1, 0),
+@pytest.mark.parametrize("H,G,D,E,window,keep", [(4, 2, 16, 24, 9, 2), (6, 2, 48, 80, 40, 5), (2, 2, 8, 8, 1, 0),
                                                  (3, 1, 10, 5, None, 0), (1, 1, 24, 130, 33, 35), (2, 1, 6, 3, 5, 1)])
 def test_sink_attention_prefill_portions_decode(dtype, H, G, D, E, window, keep):
     T = 150
@@ -323,7 +323,7 @@ def test_qk_norm_and_partial_rotation(group):
     rotated coordinates only, at positions far from 0."""
     from sglang_security_b200 import _lib
 
-    H, G, D, E, dims, base, eps = 3, 1, 10, 4, 6, 500000.0, 1e-3
+    H, G, D, E, dims, base, eps = 3, 1, 10, 4, 6, 250000.0, 1e-3
     g = torch.Generator().manual_seed(41)
     n, first = 5, 70000
     q, k, v = torch.randn(n, H * D, generator=g), torch.randn(n, G * D, generator=g), torch.randn(n, G * E, generator=g)
@@ -356,7 +356,7 @@ def test_qk_norm_and_partial_rotation(group):
 
 # ---- experts ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("E,top,ff,T", [(5, 2, 24, 3), (16, 1, 96, 150), (3, 3, 8, 1), (33, 4, 40, 70)])
+@pytest.mark.parametrize("E,top,ff,T", [(5, 2, 24, 3), (12, 1, 72, 150), (3, 3, 8, 1), (33, 4, 40, 70)])
 def test_sigmoid_router_and_scaled_input_experts(dtype, E, top, ff, T):
     from sglang_security_b200.layers.moe.fused_moe import ScaledInputExperts, TopKRouter
 
@@ -373,11 +373,11 @@ def test_sigmoid_router_and_scaled_input_experts(dtype, E, top, ff, T):
     for e in range(E):
         ex.w_up.data[e].copy_(w[f"e{e}.up"])
         ex.w_down.data[e].copy_(w[f"e{e}.down"])
-    ids, wts, _ = router(x.to(DEV))
-    s = torch.sigmoid(x.double() @ w["router"].double().t())
+    h = x.to(dtype)
+    ids, wts, _ = router(h.float().to(DEV))     # router and experts see the same values, as the oracle's do
+    s = torch.sigmoid(h.double() @ w["router"].double().t())
     assert torch.equal(ids.cpu().long().sort(-1).values, torch.topk(s, top, -1).indices.sort(-1).values)
     assert _err(wts, torch.gather(s, 1, ids.cpu().long())) <= 1e-5
-    h = x.to(dtype)
     rows = ex(h.to(DEV), ids, wts)
     got = rows.double().view(T, top, W).sum(1)
     want = P.moe(h.double(), w, "", {"router": {"experts": E, "top": top}})
