@@ -12,12 +12,17 @@
 //                        k -> norm -> rotation -> pool row; v -> pool row.  Norms and angles in fp32;
 //                        the angle is position x frequency with the frequency held as a sum of two
 //                        floats, so it is as exact at position 100000 as at position 10.
-//   sink_attn          : one CTA per (token, query head); its 4 warps take the visible keys in tiles of
-//                        32 (a lane scores one key, then the warp accumulates the tile's values column
-//                        by column), each with a running maximum and sum, merged in a fixed order at the
-//                        end.  Scores, weights and sums are fp32.  Every token walks its own list of
-//                        visible keys through req_to_token, so prompts portions and decoded tokens
-//                        of different requests mix freely in one launch.
+//   sink_attn          : one CTA per (token, key/value head); the query heads that share the key/value
+//                        head are scored together, four per pass, so their keys and values are read
+//                        once.  The CTA's 4 to 16 warps (by the longest key list) take the visible keys
+//                        in tiles of 32: a lane scores one key against the pass's heads, then the warp
+//                        accumulates the tile's values (4 columns per lane, several keys in flight), each
+//                        warp with a running maximum and sum per head, merged in warp order at the end.
+//                        Scores, weights and sums are fp32.  Every token walks its own list of visible
+//                        keys through req_to_token, so prompt portions and decoded tokens of different
+//                        requests mix freely in one launch; a token list restricts a launch to some rows.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -123,6 +128,7 @@ qk_norm_rope_write_kernel(const T* __restrict__ q, int64_t ldq, const T* __restr
 
 constexpr int kSinkMaxWarps = 16;  // warps per CTA: 4 to 16, by the longest key list (host)
 constexpr int kSinkMaxCols = 8;    // value size <= 256
+constexpr int kSinkHeads = 4;      // query heads of a key/value head scored per pass over its keys
 
 template <typename TP, typename TO>
 __global__ void __launch_bounds__(kSinkMaxWarps * 32)
@@ -132,139 +138,201 @@ sink_attn_kernel(const float* __restrict__ q, int64_t ldq, const TP* __restrict_
                  const int* __restrict__ tok_b, const float* __restrict__ sink, float scale, int window,
                  int keep_first, TO* __restrict__ out, int64_t ldo, int H, int G, int D, int E,
                  const int* __restrict__ tok_list) {
-  extern __shared__ float sink_smem[];       // q [D], then per warp: acc [E], m, l
-  const int kSinkWarps = blockDim.x >> 5;
-  float* qs = sink_smem;
-  float* wacc = qs + D;
-  float* wm = wacc + kSinkWarps * E;
-  float* wl = wm + kSinkWarps;
-  const int t = tok_list ? tok_list[blockIdx.x] : blockIdx.x, h = blockIdx.y, g = h / (H / G);
+  extern __shared__ __align__(16) float sink_smem[];
+  constexpr int RH = kSinkHeads;
+  const int nw = blockDim.x >> 5;
+  float* qs = sink_smem;                       // [RH][D] scaled queries of the pass
+  float* wacc = qs + RH * D;                   // [nw][RH][E]
+  float* wm = wacc + nw * RH * E;              // [nw][RH]
+  float* wl = wm + nw * RH;                    // [nw][RH]
+  float* wf = wl + nw * RH;                    // [nw][RH] merge factors
+  float* wt = wf + nw * RH;                    // [RH] merged denominators
+  const int t = tok_list ? tok_list[blockIdx.x] : blockIdx.x, g = blockIdx.y, R = H / G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int p = tok_pos[t];
   const int* r2t = req_to_token + req_idx[tok_b[t]] * ld_r2t;
-  for (int d = threadIdx.x; d < D; d += kSinkWarps * 32) qs[d] = q[t * ldq + h * D + d] * scale;
-  __syncthreads();
   // visible keys: the first `kf` positions, then lo .. p
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
   const int kf = min(keep_first, lo);
   const int nkeys = kf + (p - lo + 1);
-  float m = -INFINITY, l = 0.f, acc[kSinkMaxCols];
-#pragma unroll
-  for (int c = 0; c < kSinkMaxCols; ++c) acc[c] = 0.f;
   const bool vec = (D % 8 == 0) && sizeof(TP) == 2 && (ld_pool % 8 == 0) && ((k_off + g * D) % 8 == 0) &&
                    ((reinterpret_cast<uintptr_t>(pool) & 15) == 0);
   // values: 4 consecutive columns per lane with vector loads when every piece is aligned
   const bool vblk = (E % 4 == 0) && (ld_pool % 4 == 0) && ((v_off + g * E) % 4 == 0) &&
                     ((reinterpret_cast<uintptr_t>(pool) & 15) == 0);
-  for (int n0 = warp * 32; n0 < nkeys; n0 += kSinkWarps * 32) {
-    const int n = n0 + lane;
-    int64_t slot = 0;
-    float s = -INFINITY;
-    if (n < nkeys) {
-      const int j = n < kf ? n : lo + (n - kf);
-      slot = r2t[j];
-      const TP* kr = pool + slot * ld_pool + k_off + g * D;
-      float s0 = 0.f, s1 = 0.f;
-      bool done = false;
-      if constexpr (sizeof(TP) == 2) {
-#pragma unroll 4
-        for (int d = 0; vec && d < D; d += 8) {
-          const uint4 u = *reinterpret_cast<const uint4*>(kr + d);
-          const TP* e8 = reinterpret_cast<const TP*>(&u);
+  // the query heads that share this key/value head, RH at a time: their keys and values are read once
+  // per pass
+  for (int h0 = 0; h0 < R; h0 += RH) {
+    const int nr = min(RH, R - h0), hb = g * R + h0;
+    __syncthreads();                           // the previous pass has finished with the shared arrays
+    for (int i = threadIdx.x; i < RH * D; i += blockDim.x) {
+      const int r = i / D, d = i - r * D;
+      qs[i] = r < nr ? q[t * ldq + (hb + r) * D + d] * scale : 0.f;
+    }
+    __syncthreads();
+    float m[RH], l[RH], acc[RH][kSinkMaxCols];
 #pragma unroll
-          for (int i = 0; i < 8; i += 2) {
-            s0 = fmaf(qs[d + i], to_float<TP>(e8[i]), s0);
-            s1 = fmaf(qs[d + i + 1], to_float<TP>(e8[i + 1]), s1);
+    for (int r = 0; r < RH; ++r) {
+      m[r] = -INFINITY;
+      l[r] = 0.f;
+#pragma unroll
+      for (int c = 0; c < kSinkMaxCols; ++c) acc[r][c] = 0.f;
+    }
+    for (int n0 = warp * 32; n0 < nkeys; n0 += nw * 32) {
+      const int n = n0 + lane;
+      int64_t slot = 0;
+      float s[RH];
+#pragma unroll
+      for (int r = 0; r < RH; ++r) s[r] = 0.f;
+      if (n < nkeys) {
+        const int j = n < kf ? n : lo + (n - kf);
+        slot = r2t[j];
+        const TP* kr = pool + slot * ld_pool + k_off + g * D;
+        bool done = false;
+        if constexpr (sizeof(TP) == 2) {
+#pragma unroll 2
+          for (int d = 0; vec && d < D; d += 8) {
+            const uint4 u = *reinterpret_cast<const uint4*>(kr + d);
+            const TP* e8 = reinterpret_cast<const TP*>(&u);
+            float kv[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) kv[i] = to_float<TP>(e8[i]);
+#pragma unroll
+            for (int r = 0; r < RH; ++r) {
+              const float4 q0 = *reinterpret_cast<const float4*>(qs + r * D + d);
+              const float4 q1 = *reinterpret_cast<const float4*>(qs + r * D + d + 4);
+              s[r] = fmaf(q0.x, kv[0], s[r]);
+              s[r] = fmaf(q0.y, kv[1], s[r]);
+              s[r] = fmaf(q0.z, kv[2], s[r]);
+              s[r] = fmaf(q0.w, kv[3], s[r]);
+              s[r] = fmaf(q1.x, kv[4], s[r]);
+              s[r] = fmaf(q1.y, kv[5], s[r]);
+              s[r] = fmaf(q1.z, kv[6], s[r]);
+              s[r] = fmaf(q1.w, kv[7], s[r]);
+            }
+          }
+          done = vec;
+        }
+        if (!done) {
+          for (int d = 0; d < D; ++d) {
+            const float kd = to_float<TP>(kr[d]);
+#pragma unroll
+            for (int r = 0; r < RH; ++r) s[r] = fmaf(qs[r * D + d], kd, s[r]);
           }
         }
-        done = vec;
       }
-      if (!done) {
-        int d = 0;
-        for (; d + 1 < D; d += 2) {
-          s0 = fmaf(qs[d], to_float<TP>(kr[d]), s0);
-          s1 = fmaf(qs[d + 1], to_float<TP>(kr[d + 1]), s1);
-        }
-        if (d < D) s0 = fmaf(qs[d], to_float<TP>(kr[d]), s0);
+      float pj[RH];
+#pragma unroll
+      for (int r = 0; r < RH; ++r) {
+        const float sr = n < nkeys ? s[r] : -INFINITY;
+        float tm = sr;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, o));
+        const float mn = fmaxf(m[r], tm);
+        const float corr = expf(m[r] - mn);       // m = -inf on the first tile: exp(-inf) = 0
+        pj[r] = n < nkeys ? expf(sr - mn) : 0.f;
+        float ps = pj[r];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+        l[r] = l[r] * corr + ps;
+        m[r] = mn;
+#pragma unroll
+        for (int c = 0; c < kSinkMaxCols; ++c) acc[r][c] *= corr;
       }
-      s = s0 + s1;
-    }
-    float tm = s;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, o));
-    const float mn = fmaxf(m, tm);
-    const float corr = expf(m - mn);          // m = -inf on the first tile: exp(-inf) = 0
-    const float pj = n < nkeys ? expf(s - mn) : 0.f;
-    float ps = pj;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
-    l = l * corr + ps;
-    m = mn;
-#pragma unroll
-    for (int c = 0; c < kSinkMaxCols; ++c) acc[c] *= corr;
-    const int cnt = min(32, nkeys - n0);
-    // unrolled so that the value rows of several keys are in flight at once (a rolled loop waits a
-    // full memory round trip per key)
-#pragma unroll 8
-    for (int jj = 0; jj < 32; ++jj) {
-      if (jj >= cnt) break;
-      const float pw = __shfl_sync(0xffffffffu, pj, jj);
-      const int64_t sl = __shfl_sync(0xffffffffu, slot, jj);
-      const TP* vr = pool + sl * ld_pool + v_off + g * E;
+      const int cnt = min(32, nkeys - n0);
       if (vblk) {
-        // a lane owns 4 consecutive columns per 128: one 8-byte (16-bit pool) or 16-byte load each
+        // a lane owns 4 consecutive columns per 128: one 8-byte (16-bit pool) or 16-byte load per key;
+        // the rows of 8 keys are requested before the first is used (a loop that loads and uses one key
+        // at a time waits a full memory round trip per key)
+        using V4 = typename std::conditional<sizeof(TP) == 2, uint2, float4>::type;
 #pragma unroll
         for (int c = 0; c < kSinkMaxCols / 4; ++c) {
+          if (128 * c >= E) continue;            // the same for all lanes: they shuffle together below
           const int e = 128 * c + 4 * lane;
-          if (e < E) {
-            float x[4];
-            if constexpr (sizeof(TP) == 2) {
-              const uint2 u = *reinterpret_cast<const uint2*>(vr + e);
-              const TP* t4 = reinterpret_cast<const TP*>(&u);
+          const bool col_ok = e < E;
+          for (int j0 = 0; j0 < cnt; j0 += 8) {
+            V4 u[8];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) x[i] = to_float<TP>(t4[i]);
-            } else {
-              const float4 u = *reinterpret_cast<const float4*>(vr + e);
-              x[0] = u.x, x[1] = u.y, x[2] = u.z, x[3] = u.w;
+            for (int i = 0; i < 8; ++i) {
+              const int64_t sl = __shfl_sync(0xffffffffu, slot, (j0 + i) & 31);   // lanes past cnt hold slot 0
+              u[i] = *reinterpret_cast<const V4*>(pool + sl * ld_pool + v_off + g * E + (col_ok ? e : 0));
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[4 * c + i] = fmaf(pw, x[i], acc[4 * c + i]);
+            for (int i = 0; i < 8; ++i) {
+              float x[4];
+              if constexpr (sizeof(TP) == 2) {
+                const TP* t4 = reinterpret_cast<const TP*>(&u[i]);
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4) x[k4] = to_float<TP>(t4[k4]);
+              } else {
+                const float* f4 = reinterpret_cast<const float*>(&u[i]);
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4) x[k4] = f4[k4];
+              }
+              const bool live = col_ok && j0 + i < cnt;
+#pragma unroll
+              for (int r = 0; r < RH; ++r) {
+                const float pw = __shfl_sync(0xffffffffu, pj[r], (j0 + i) & 31);
+                if (live) {
+#pragma unroll
+                  for (int k4 = 0; k4 < 4; ++k4) acc[r][4 * c + k4] = fmaf(pw, x[k4], acc[r][4 * c + k4]);
+                }
+              }
+            }
           }
         }
       } else {
+        for (int jj = 0; jj < cnt; ++jj) {
+          const int64_t sl = __shfl_sync(0xffffffffu, slot, jj);
+          float pw[RH];
 #pragma unroll
-        for (int c = 0; c < kSinkMaxCols; ++c) {
-          const int e = lane + 32 * c;
-          if (e < E) acc[c] = fmaf(pw, to_float<TP>(vr[e]), acc[c]);
+          for (int r = 0; r < RH; ++r) pw[r] = __shfl_sync(0xffffffffu, pj[r], jj);
+          const TP* vr = pool + sl * ld_pool + v_off + g * E;
+#pragma unroll
+          for (int c = 0; c < kSinkMaxCols; ++c) {
+            const int e = lane + 32 * c;
+            if (e < E) {
+              const float x = to_float<TP>(vr[e]);
+#pragma unroll
+              for (int r = 0; r < RH; ++r) acc[r][c] = fmaf(pw[r], x, acc[r][c]);
+            }
+          }
         }
       }
     }
-  }
-  if (lane == 0) {
-    wm[warp] = m;
-    wl[warp] = l;
-  }
+    // per-warp partial softmaxes -> shared memory, merged in warp order
 #pragma unroll
-  for (int c = 0; c < kSinkMaxCols; ++c) {
-    const int e = vblk ? 128 * (c / 4) + 4 * lane + (c & 3) : lane + 32 * c;
-    if (e < E) wacc[warp * E + e] = acc[c];
-  }
-  __syncthreads();
-  float mt = sink ? sink[h] : -INFINITY;
-  for (int w = 0; w < kSinkWarps; ++w) mt = fmaxf(mt, wm[w]);
-  float lt = sink ? expf(sink[h] - mt) : 0.f;
-  float f[kSinkMaxWarps];
+    for (int r = 0; r < RH; ++r) {
+      if (lane == 0) {
+        wm[warp * RH + r] = m[r];
+        wl[warp * RH + r] = l[r];
+      }
 #pragma unroll
-  for (int w = 0; w < kSinkMaxWarps; ++w) {
-    f[w] = (w < kSinkWarps && wm[w] != -INFINITY) ? expf(wm[w] - mt) : 0.f;
-    if (w < kSinkWarps) lt = fmaf(wl[w], f[w], lt);
-  }
-  for (int e = threadIdx.x; e < E; e += kSinkWarps * 32) {
-    float o = 0.f;
-#pragma unroll
-    for (int w = 0; w < kSinkMaxWarps; ++w)
-      if (w < kSinkWarps) o = fmaf(wacc[w * E + e], f[w], o);
-    out[t * ldo + h * E + e] = from_float<TO>(o / lt);
+      for (int c = 0; c < kSinkMaxCols; ++c) {
+        const int e = vblk ? 128 * (c / 4) + 4 * lane + (c & 3) : lane + 32 * c;
+        if (e < E) wacc[(warp * RH + r) * E + e] = acc[r][c];
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < nr) {
+      const int r = threadIdx.x;
+      float mt = sink ? sink[hb + r] : -INFINITY;
+      for (int w = 0; w < nw; ++w) mt = fmaxf(mt, wm[w * RH + r]);
+      float lt = sink ? expf(sink[hb + r] - mt) : 0.f;
+      for (int w = 0; w < nw; ++w) {
+        const float f = wm[w * RH + r] == -INFINITY ? 0.f : expf(wm[w * RH + r] - mt);
+        wf[w * RH + r] = f;
+        lt = fmaf(wl[w * RH + r], f, lt);
+      }
+      wt[r] = lt;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nr * E; i += blockDim.x) {
+      const int r = i / E, e = i - r * E;
+      float o = 0.f;
+      for (int w = 0; w < nw; ++w) o = fmaf(wacc[(w * RH + r) * E + e], wf[w * RH + r], o);
+      out[t * ldo + (hb + r) * E + e] = from_float<TO>(o / wt[r]);
+    }
   }
 }
 
@@ -320,19 +388,24 @@ extern "C" int b200_sink_attn(const float* q, int64_t ldq, const void* pool, int
   B200_REQUIRE(q && pool && req_to_token && req_idx && tok_pos && tok_b && out,
                "b200_sink_attn: null pointer");
   B200_REQUIRE(T > 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && E > 0 && E <= 32 * kSinkMaxCols &&
-                   window >= 0 && keep_first >= 0,
+                   window >= 0 && keep_first >= 0 && G <= 65535,
                "b200_sink_attn: heads %d / %d, key size %d, value size %d (max %d)", H, G, D, E,
                32 * kSinkMaxCols);
   // one warp per 64 keys of the longest list (a hint; 0 = unknown): a warp's tiles are dependent round
   // trips to memory (slots, keys, values), so long lists want many warps and short ones few
-  const int kSinkWarps = max_keys <= 0 ? 4 : min(kSinkMaxWarps, max(4, ceil_div(max_keys, 64)));
-  const size_t smem = sizeof(float) * (D + kSinkWarps * (E + 2));
+  int nw = max_keys <= 0 ? 4 : min(kSinkMaxWarps, max(4, ceil_div(max_keys, 64)));
+  auto smem_for = [&](int w) {
+    return sizeof(float) * (static_cast<size_t>(kSinkHeads) * D + static_cast<size_t>(w) * kSinkHeads * (E + 3) +
+                            kSinkHeads + 4);
+  };
+  while (nw > 1 && smem_for(nw) > 48 * 1024) nw >>= 1;
+  const size_t smem = smem_for(nw);
   B200_REQUIRE(smem <= 48 * 1024, "b200_sink_attn: key size %d too large", D);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   ScopedKernelTimer timer("sink_attn", st);
-  const dim3 grid(T, H);
+  const dim3 grid(T, G);
 #define LAUNCH(TT)                                                                                   \
-  launch_kernel(sink_attn_kernel<TT, TT>, grid, dim3(kSinkWarps * 32), smem, st, 1, 0, q, ldq,       \
+  launch_kernel(sink_attn_kernel<TT, TT>, grid, dim3(nw * 32), smem, st, 1, 0, q, ldq,               \
                 static_cast<const TT*>(pool), ld_pool, k_off, v_off, req_to_token, ld_r2t, req_idx,  \
                 tok_pos, tok_b, sink, scale, window, keep_first, static_cast<TT*>(out), ldo, H, G, D, \
                 E, tok_list)
