@@ -51,8 +51,10 @@ moe_route_kernel(const T* __restrict__ h, int64_t ldh, const float* __restrict__
 #pragma unroll
           for (int k = 0; k < 8; ++k) hv[k] = to_float<T>(e[k]);
         } else {
-#pragma unroll
-          for (int k = 0; k < 8; ++k) hv[k] = to_float<T>(row[d + k]);
+          const float4 h0 = *reinterpret_cast<const float4*>(row + d);
+          const float4 h1 = *reinterpret_cast<const float4*>(row + d + 4);
+          hv[0] = h0.x, hv[1] = h0.y, hv[2] = h0.z, hv[3] = h0.w;
+          hv[4] = h1.x, hv[5] = h1.y, hv[6] = h1.z, hv[7] = h1.w;
         }
         const float4 w0 = *reinterpret_cast<const float4*>(w + d);
         const float4 w1 = *reinterpret_cast<const float4*>(w + d + 4);
