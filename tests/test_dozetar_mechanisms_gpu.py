@@ -236,7 +236,8 @@ def _qkv(T, H, G, D, E, seed, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,D,E,window,keep", [(4, 2, 16, 24, 9, 2), (6, 2, 48, 80, 40, 5), (2, 2, 8, 8, 1, 0),
-                                                 (3, 1, 10, 5, None, 0), (1, 1, 24, 130, 33, 35), (2, 1, 6, 3, 5, 1)])
+                                                 (3, 1, 10, 5, None, 0), (1, 1, 24, 130, 33, 35), (2, 1, 6, 3, 5, 1),
+                                                 (10, 1, 12, 20, 17, 3), (16, 2, 8, 8, 64, 0)])
 def test_sink_attention_prefill_portions_decode(dtype, H, G, D, E, window, keep):
     T = 150
     q, k, v = _qkv(T, H, G, D, E, 11, dtype)
