@@ -134,7 +134,7 @@ class DozetarForCausalLM(nn.Module):
             raise ValueError(f"checkpoint lacks {len(missing)} tensors, e.g. {sorted(missing)[:4]}")
 
     def _load_layer_tensor(self, layer: DozetarLayer, key: str, w: torch.Tensor) -> None:
-        lid, H = layer.layer_id, None
+        lid = layer.layer_id
         bad = ValueError(f"unexpected tensor l{lid}.{key}")
         if key == "norm1":
             layer.norm1.weight.data.copy_(w.float())

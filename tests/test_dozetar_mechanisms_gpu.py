@@ -2,8 +2,6 @@
 output-normed residual add, the logit cap, the gated group norm, the two matrix-state recurrences
 (steps, slots, odd sizes), the sink attention (windows, kept first tokens, pages, far keys) and the
 sigmoid-scored experts whose weight scales their input."""
-import math
-
 import pytest
 import torch
 
